@@ -58,6 +58,18 @@ class CacheGroup:
     def window(self) -> int | None:
         return self.spec.window if self.spec.kind == "window" else None
 
+    @property
+    def chunk(self) -> int | None:
+        return self.spec.chunk if self.spec.kind == "chunk" else None
+
+    def first_needed_key(self, length: int) -> int:
+        """The lowest position that a query at position ``length`` or later can still read."""
+        if self.window is not None:
+            return max(0, length - self.window + 1)
+        if self.chunk is not None:
+            return length // self.chunk * self.chunk
+        return 0
+
     def bytes_per_page(self, element_size: int) -> int:
         per_token = sum(t.heads * t.width for t in self.spec.stored())
         return len(self.positions) * per_token * self.page_size * element_size
@@ -107,8 +119,10 @@ class CacheManager:
                 self._position_group.append(None)
                 self._position_slot.append(None)
                 continue
-            if spec.kind not in ("full", "window"):
+            if spec.kind not in ("full", "window", "chunk"):
                 raise ValueError(f"schedule position {pos}: unknown cache kind {spec.kind!r}")
+            if spec.kind == "chunk" and (spec.chunk is None or spec.chunk <= 0):
+                raise ValueError(f"schedule position {pos}: a chunk cache needs a positive chunk")
             if spec.kind == "window" and (spec.window is None or spec.window <= 0):
                 raise ValueError(f"schedule position {pos}: a window cache needs a positive window")
             stored = spec.stored()
@@ -199,14 +213,15 @@ class CacheManager:
             seq.pages[g.index].extend(g.pool.allocate_many(n))
 
     def commit(self, seq: SequenceCache, num_tokens: int) -> None:
-        """The step wrote ``num_tokens`` more positions.  Pages wholly behind every window are given back."""
+        """The step wrote ``num_tokens`` more positions.  Pages wholly behind every window, or wholly before the block
+        of positions that the next query lies in, are given back."""
         seq.length += num_tokens
         for g in self.groups:
-            if g.window is None:
+            if g.window is None and g.chunk is None:
                 continue
-            # the next query is at position >= length and sees keys > position - window
-            first_needed_key = seq.length - g.window + 1
-            releasable = max(0, first_needed_key) // self.page_size
+            # the next query is at position >= length: with a window it sees keys > position - window, with blocks
+            # the keys from its block's first position on
+            releasable = g.first_needed_key(seq.length) // self.page_size
             pages = seq.pages[g.index]
             for logical in range(seq.first_live[g.index], min(releasable, len(pages))):
                 if pages[logical] >= 0:
@@ -264,10 +279,11 @@ class CacheManager:
         out = []
         full = (num_tokens + self.page_size - 1) // self.page_size
         for g in self.groups:
-            if g.window is None or chunk <= 0:
+            reach = g.window if g.window is not None else g.chunk
+            if reach is None or chunk <= 0:
                 out.append(full)
             else:
-                span = g.window + chunk + self.page_size  # window behind, the step's tokens, a partial page
+                span = reach + chunk + self.page_size  # what is still read, the step's tokens, a partial page
                 out.append(min(full, (span + self.page_size - 1) // self.page_size + 1))
         return out
 

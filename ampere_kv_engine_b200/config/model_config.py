@@ -203,3 +203,129 @@ def read_config_json(model_dir: str) -> dict[str, Any]:
         if isinstance(gen, dict) and gen.get("eos_token_id") is not None:
             raw["eos_token_id"] = gen["eos_token_id"]
     return raw
+
+
+def _section(d: dict, key: str, where: str) -> dict:
+    if key not in d or not isinstance(d[key], dict):
+        raise ConfigError(f"config.json: {where}'{key}' must be an object")
+    return d[key]
+
+
+def _sized(d: dict, key: str, where: str) -> int:
+    if key not in d:
+        raise ConfigError(f"config.json: {where}required key '{key}' is missing")
+    value = d[key]
+    if isinstance(value, bool) or not isinstance(value, int) or value <= 0:
+        raise ConfigError(f"config.json: {where}'{key}' must be a positive integer, got {value!r}")
+    return value
+
+
+def _number(d: dict, key: str, where: str) -> float:
+    if key not in d:
+        raise ConfigError(f"config.json: {where}required key '{key}' is missing")
+    value = d[key]
+    if isinstance(value, bool) or not isinstance(value, (int, float)):
+        raise ConfigError(f"config.json: {where}'{key}' must be a number, got {value!r}")
+    return float(value)
+
+
+@dataclass(frozen=True)
+class SukalornLayer:
+    """One entry of ``layers``: the mixer's ``type``, its sizes and constants as config.json gives them, and the
+    feed-forward (None: the layer has none)."""
+
+    type: str
+    mixer: dict
+    mlp: dict | None
+
+    MIXERS = ("attention", "latent_attention")
+
+
+@dataclass(frozen=True)
+class SukalornConfig:
+    """config.json of the ``Sukalorn`` decoder: ``vocab``, ``width``, ``norm.eps`` and a list of layers, each naming
+    its mixer (``attention``: grouped queries with unit-norm q/k, capped and distance-biased scores, blocks of
+    positions, blended values and a gate per head; ``latent_attention``: low-rank query and key/value latents with a
+    shared rotated key part) and its dense feed-forward.  Every size and constant is read from here."""
+
+    vocab: int
+    width: int
+    norm_eps: float
+    layers: tuple[SukalornLayer, ...]
+    max_position_embeddings: int = 1 << 20
+    eos_token_id: tuple[int, ...] = ()
+    architectures: tuple[str, ...] = ("Sukalorn",)
+
+    ARCHITECTURE = "Sukalorn"
+
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @classmethod
+    def from_dict(cls, d: dict[str, Any]) -> "SukalornConfig":
+        layers_raw = d.get("layers")
+        if not isinstance(layers_raw, (list, tuple)) or not layers_raw:
+            raise ConfigError("config.json: key 'layers' must be a non-empty list")
+        layers = []
+        for i, entry in enumerate(layers_raw):
+            where = f"layers[{i}]: "
+            if not isinstance(entry, dict) or entry.get("type") not in SukalornLayer.MIXERS:
+                raise ConfigError(f"config.json: {where}'type' must be one of {list(SukalornLayer.MIXERS)}, "
+                                  f"got {entry.get('type') if isinstance(entry, dict) else entry!r}")
+            mixer = _section(entry, "mixer", where)
+            where_m = where + "mixer: "
+            for key in ("heads", "dim", "vdim"):
+                _sized(mixer, key, where_m)
+            _number(mixer, "scale", where_m)
+            if entry["type"] == "attention":
+                kv = _sized(mixer, "kv_heads", where_m)
+                if mixer["heads"] % kv:
+                    raise ConfigError(f"config.json: {where_m}'heads' ({mixer['heads']}) must be a multiple of "
+                                      f"'kv_heads' ({kv})")
+                if mixer.get("softcap") is not None and _number(mixer, "softcap", where_m) <= 0:
+                    raise ConfigError(f"config.json: {where_m}'softcap' must be positive")
+                if mixer.get("mask") is not None:
+                    _sized(_section(mixer, "mask", where_m), "size", where_m + "mask: ")
+            else:
+                for key in ("q_rank", "kv_rank", "rot_dim"):
+                    _sized(mixer, key, where_m)
+                rot = _section(mixer, "rot", where_m)
+                dims = _sized(rot, "dims", where_m + "rot: ")
+                if _number(rot, "base", where_m + "rot: ") <= 0:
+                    raise ConfigError(f"config.json: {where_m}rot: 'base' must be positive")
+                if dims % 2 or dims > mixer["rot_dim"]:
+                    raise ConfigError(f"config.json: {where_m}rot: 'dims' must be even and at most 'rot_dim' "
+                                      f"({mixer['rot_dim']}), got {dims}")
+            mlp = entry.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict):
+                    raise ConfigError(f"config.json: {where}'mlp' must be an object or null")
+                if mlp.get("kind", "dense") != "dense":
+                    raise ConfigError(f"config.json: {where}mlp: 'kind' must be 'dense', got {mlp.get('kind')!r}")
+                _sized(mlp, "ff", where + "mlp: ")
+            layers.append(SukalornLayer(entry["type"], dict(mixer), None if mlp is None else dict(mlp)))
+        eos = d.get("eos_token_id")
+        eos = () if eos is None else ((eos,) if isinstance(eos, int) else tuple(eos))
+        cfg = cls(
+            vocab=_sized(d, "vocab", ""),
+            width=_sized(d, "width", ""),
+            norm_eps=_number(_section(d, "norm", ""), "eps", "norm: "),
+            layers=tuple(layers),
+            max_position_embeddings=_optional(d, "max_position_embeddings", int, 1 << 20),
+            eos_token_id=eos,
+        )
+        if cfg.norm_eps <= 0:
+            raise ConfigError("config.json: norm: 'eps' must be positive")
+        return cfg
+
+    def to_dict(self) -> dict[str, Any]:
+        out = {"architecture": self.ARCHITECTURE, "vocab": self.vocab, "width": self.width,
+               "norm": {"eps": self.norm_eps},
+               "layers": [{"type": l.type, "mixer": dict(l.mixer), "mlp": None if l.mlp is None else dict(l.mlp)}
+                          for l in self.layers]}
+        if self.max_position_embeddings != 1 << 20:
+            out["max_position_embeddings"] = self.max_position_embeddings
+        if self.eos_token_id:
+            out["eos_token_id"] = list(self.eos_token_id)
+        return out

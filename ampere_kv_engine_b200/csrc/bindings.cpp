@@ -687,6 +687,246 @@ void paged_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cac
   check_launch(akv::launch_paged_attention(p, stream_of(q)), "paged_attention");
 }
 
+// A paged storage of rows: [pages, heads, page_size, width], contiguous.
+void check_pages(const Tensor& cache, const char* name, int64_t heads, int64_t min_width, const Tensor& like) {
+  check_cuda(cache, name);
+  check_same(cache, like, name, "activations");
+  AKV_CHECK(cache.dim() == 4 && cache.size(1) == heads && cache.size(3) >= min_width, name,
+            " must be [pages, ", heads, " heads, page_size, at least ", min_width, " elements]");
+}
+
+// Attention with reshaped scores and keys / values of different widths (see launchers.h).  k_cache
+// [pages, kv heads, page_size, >= key width]; v_cache likewise for the value width, or the same tensor when a value
+// is the first v_dim elements of its key row.
+void scored_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, Tensor& out,
+                      const Tensor& block_table, const Tensor& cu_q, const Tensor& ctx_lens, const Tensor& tile_seq,
+                      const Tensor& tile_q0, const Tensor& tile_nq, const OptTensor& partials, int64_t num_tiles,
+                      int64_t q_tile, int64_t num_splits, int64_t num_heads, int64_t num_kv_heads, int64_t v_dim,
+                      int64_t window, int64_t chunk, double scale, double softcap, const OptTensor& slopes,
+                      const OptTensor& gate, const OptTensor& status) {
+  check_cuda(q, "q");
+  check_cuda(out, "out");
+  check_same(q, out, "q", "out");
+  AKV_CHECK(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0,
+            "scored_attention: heads (", num_heads, ") must be a positive multiple of kv heads (", num_kv_heads, ")");
+  AKV_CHECK(q.dim() == 2 && q.size(1) % num_heads == 0, "q must be [tokens, heads * key width]");
+  const int64_t n = q.size(0), d = q.size(1) / num_heads;
+  AKV_CHECK(d >= 1 && d <= 1024, "scored_attention: the key width must be between 1 and 1024, got ", d);
+  AKV_CHECK(v_dim >= 1 && v_dim <= 512, "scored_attention: the value width must be between 1 and 512, got ", v_dim);
+  AKV_CHECK(out.dim() == 2 && out.size(0) == n && out.size(1) == num_heads * v_dim,
+            "out must be [tokens, heads * value width]");
+  check_pages(k_cache, "k_cache", num_kv_heads, d, q);
+  check_pages(v_cache, "v_cache", num_kv_heads, v_dim, q);
+  AKV_CHECK(k_cache.size(0) == v_cache.size(0) && k_cache.size(2) == v_cache.size(2),
+            "k_cache and v_cache must have the same pages and page size");
+  check_i32(block_table, "block_table");
+  AKV_CHECK(block_table.dim() == 2, "block_table must be [sequences, width]");
+  const int64_t s = block_table.size(0);
+  check_i32(cu_q, "cu_q", s + 1);
+  check_i32(ctx_lens, "ctx_lens", s);
+  AKV_CHECK(num_tiles >= 0 && q_tile >= 1 && num_splits >= 1 && window >= 0 && chunk >= 0 && softcap >= 0,
+            "bad tile / split / window / chunk / softcap");
+  check_i32(tile_seq, "tile_seq", num_tiles);
+  check_i32(tile_q0, "tile_q0", num_tiles);
+  check_i32(tile_nq, "tile_nq", num_tiles);
+  akv::ScoredAttentionParams sp{};
+  akv::PagedAttentionParams& p = sp.base;
+  if (num_splits > 1) {
+    AKV_CHECK(partials.has_value(), "num_splits > 1 needs a partials workspace");
+    check_cuda(*partials, "partials");
+    AKV_CHECK(partials->scalar_type() == at::kFloat && partials->numel() >= n * num_heads * num_splits * (v_dim + 2),
+              "partials must be float32 with at least tokens * heads * splits * (value width + 2) entries");
+    p.partials = partials->data_ptr<float>();
+  }
+  if (slopes.has_value()) {
+    check_f32(*slopes, "slopes", num_heads);
+    sp.slopes = slopes->data_ptr<float>();
+  }
+  if (gate.has_value()) {
+    check_f32(*gate, "gate", n * num_heads);
+    sp.gate = gate->data_ptr<float>();
+  }
+  p.q = q.data_ptr();
+  p.k_cache = k_cache.data_ptr();
+  p.v_cache = v_cache.data_ptr();
+  p.out = out.data_ptr();
+  p.block_table = block_table.data_ptr<int>();
+  p.cu_q = cu_q.data_ptr<int>();
+  p.ctx_lens = ctx_lens.data_ptr<int>();
+  p.tile_seq = tile_seq.data_ptr<int>();
+  p.tile_q0 = tile_q0.data_ptr<int>();
+  p.tile_nq = tile_nq.data_ptr<int>();
+  p.num_tokens = n;
+  p.num_tiles = (int)num_tiles;
+  p.q_tile = (int)q_tile;
+  p.num_splits = (int)num_splits;
+  p.num_seqs = (int)s;
+  p.table_width = (int)block_table.size(1);
+  p.num_heads = (int)num_heads;
+  p.num_kv_heads = (int)num_kv_heads;
+  p.head_dim = (int)d;
+  p.page_size = (int)k_cache.size(2);
+  p.num_pages = k_cache.size(0);
+  p.window = (int)window;
+  p.kernel = 1;
+  p.scale = (float)scale;
+  p.dtype = dtype_code(q, "q");
+  p.status = status_ptr(status);
+  sp.v_dim = (int)v_dim;
+  sp.k_row_stride = k_cache.size(3);
+  sp.v_row_stride = v_cache.size(3);
+  sp.softcap = (float)softcap;
+  sp.chunk = (int)chunk;
+  c10::cuda::CUDAGuard guard(q.device());
+  check_launch(akv::launch_scored_attention(sp, stream_of(q)), "scored_attention");
+}
+
+void head_prep(const Tensor& x, const OptTensor& slots, Tensor& q_out, const OptTensor& k_cache,
+               const OptTensor& v_cache, const OptTensor& v_keep, const OptTensor& v_other,
+               const OptTensor& blend_weight, const OptTensor& gate_out, int64_t num_heads, int64_t num_kv_heads,
+               int64_t head_dim, int64_t v_dim, bool unit_norm, double eps, const OptTensor& status) {
+  check_cuda(x, "x");
+  check_cuda(q_out, "q_out");
+  check_same(x, q_out, "x", "q_out");
+  AKV_CHECK(num_heads > 0 && num_kv_heads > 0 && head_dim > 0 && v_dim > 0, "head_prep: sizes must be positive");
+  const int64_t width = num_heads * head_dim + num_kv_heads * (head_dim + v_dim) + (gate_out.has_value() ? num_heads : 0);
+  AKV_CHECK(x.dim() == 2 && x.size(1) == width, "x must be [tokens, ", width, "], the q, k, v (and gate) columns");
+  const int64_t n = x.size(0);
+  AKV_CHECK(q_out.numel() == n * num_heads * head_dim, "q_out must be [tokens, heads * head_dim]");
+  akv::HeadPrepParams p{};
+  p.x = x.data_ptr();
+  p.q_out = q_out.data_ptr();
+  if (slots.has_value()) {
+    check_i32(*slots, "slots", n);
+    p.slots = slots->data_ptr<int>();
+  }
+  if (k_cache.has_value()) {
+    AKV_CHECK(v_cache.has_value() && slots.has_value(), "k_cache needs v_cache and slots");
+    check_pages(*k_cache, "k_cache", num_kv_heads, head_dim, x);
+    check_pages(*v_cache, "v_cache", num_kv_heads, v_dim, x);
+    AKV_CHECK(k_cache->size(0) == v_cache->size(0) && k_cache->size(2) == v_cache->size(2),
+              "k_cache and v_cache must have the same pages and page size");
+    p.k_cache = k_cache->data_ptr();
+    p.v_cache = v_cache->data_ptr();
+    p.page_size = (int)k_cache->size(2);
+    p.num_pages = k_cache->size(0);
+    p.k_row_stride = k_cache->size(3);
+    p.v_row_stride = v_cache->size(3);
+  }
+  auto dense_v = [&](const OptTensor& t, const char* name) -> void* {
+    if (!t.has_value()) return nullptr;
+    check_cuda(*t, name);
+    check_same(*t, x, name, "x");
+    AKV_CHECK(t->numel() == n * num_kv_heads * v_dim, name, " must be [tokens, kv heads * value width]");
+    return t->data_ptr();
+  };
+  p.v_keep = dense_v(v_keep, "v_keep");
+  p.v_other = dense_v(v_other, "v_other");
+  if (v_other.has_value()) {
+    AKV_CHECK(blend_weight.has_value(), "v_other needs blend_weight");
+    check_f32(*blend_weight, "blend_weight", 1);
+    p.blend_weight = blend_weight->data_ptr<float>();
+  }
+  if (gate_out.has_value()) {
+    check_f32(*gate_out, "gate_out", n * num_heads);
+    p.gate_out = gate_out->data_ptr<float>();
+  }
+  p.num_tokens = n;
+  p.num_heads = (int)num_heads;
+  p.num_kv_heads = (int)num_kv_heads;
+  p.head_dim = (int)head_dim;
+  p.v_dim = (int)v_dim;
+  p.unit_norm = unit_norm ? 1 : 0;
+  p.eps = (float)eps;
+  p.dtype = dtype_code(x, "x");
+  p.status = status_ptr(status);
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_head_prep(p, stream_of(x)), "head_prep");
+}
+
+void latent_prep(const Tensor& x, const Tensor& positions, const OptTensor& slots, const Tensor& q_weight,
+                 const Tensor& kv_weight, const Tensor& inv_freq, Tensor& q_latent, const OptTensor& cache,
+                 int64_t q_rank, int64_t kv_rank, int64_t rot_dim, int64_t rotary_dims, double eps,
+                 const OptTensor& status) {
+  check_cuda(x, "x");
+  check_cuda(q_latent, "q_latent");
+  check_same(x, q_latent, "x", "q_latent");
+  AKV_CHECK(q_rank > 0 && kv_rank > 0 && rot_dim >= 0 && rotary_dims >= 0 && rotary_dims <= rot_dim &&
+                rotary_dims % 2 == 0,
+            "latent_prep: ranks must be positive and rotary_dims an even number up to rot_dim");
+  AKV_CHECK(x.dim() == 2 && x.size(1) == q_rank + kv_rank + rot_dim,
+            "x must be [tokens, q_rank + kv_rank + rot_dim]");
+  const int64_t n = x.size(0);
+  check_i32(positions, "positions", n);
+  check_f32(q_weight, "q_weight", q_rank);
+  check_f32(kv_weight, "kv_weight", kv_rank);
+  check_f32(inv_freq, "inv_freq", rotary_dims / 2);
+  AKV_CHECK(q_latent.numel() == n * q_rank, "q_latent must be [tokens, q_rank]");
+  akv::LatentPrepParams p{};
+  p.x = x.data_ptr();
+  p.positions = positions.data_ptr<int>();
+  if (slots.has_value()) {
+    check_i32(*slots, "slots", n);
+    p.slots = slots->data_ptr<int>();
+  }
+  p.q_weight = q_weight.data_ptr<float>();
+  p.kv_weight = kv_weight.data_ptr<float>();
+  p.inv_freq = inv_freq.data_ptr<float>();
+  p.q_latent = q_latent.data_ptr();
+  if (cache.has_value()) {
+    AKV_CHECK(slots.has_value(), "cache needs slots");
+    check_pages(*cache, "cache", 1, kv_rank + rot_dim, x);
+    p.cache = cache->data_ptr();
+    p.page_size = (int)cache->size(2);
+    p.num_pages = cache->size(0);
+    p.row_stride = cache->size(3);
+  }
+  p.num_tokens = n;
+  p.q_rank = (int)q_rank;
+  p.kv_rank = (int)kv_rank;
+  p.rot_dim = (int)rot_dim;
+  p.rotary_dims = (int)rotary_dims;
+  p.eps = (float)eps;
+  p.dtype = dtype_code(x, "x");
+  p.status = status_ptr(status);
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_latent_prep(p, stream_of(x)), "latent_prep");
+}
+
+void rotate_pairs(const Tensor& in, Tensor& out, const Tensor& positions, const Tensor& inv_freq, int64_t heads,
+                  int64_t cols, int64_t rotary_dims, int64_t in_offset, int64_t out_offset) {
+  check_cuda(in, "in");
+  check_cuda(out, "out");
+  check_same(in, out, "in", "out");
+  AKV_CHECK(in.dim() == 2 && out.dim() == 2 && in.size(0) == out.size(0) && heads > 0 && in.size(1) % heads == 0 &&
+                out.size(1) % heads == 0,
+            "in and out must be [tokens, heads * width]");
+  const int64_t n = in.size(0), in_width = in.size(1) / heads, out_width = out.size(1) / heads;
+  AKV_CHECK(cols >= 0 && in_offset >= 0 && out_offset >= 0 && in_offset + cols <= in_width &&
+                out_offset + cols <= out_width && rotary_dims >= 0 && rotary_dims <= cols && rotary_dims % 2 == 0,
+            "rotate_pairs: the column range must lie inside both tensors and rotary_dims be even and inside it");
+  check_i32(positions, "positions", n);
+  check_f32(inv_freq, "inv_freq", rotary_dims / 2);
+  c10::cuda::CUDAGuard guard(in.device());
+  check_launch(akv::launch_rotate_pairs(in.data_ptr(), out.data_ptr(), positions.data_ptr<int>(),
+                                        inv_freq.data_ptr<float>(), n, (int)heads, (int)cols, (int)rotary_dims,
+                                        in_width, (int)in_offset, out_width, (int)out_offset, dtype_code(in, "in"),
+                                        stream_of(in)),
+               "rotate_pairs");
+}
+
+void activation(const Tensor& in, Tensor& out, int64_t kind) {
+  check_cuda(in, "in");
+  check_cuda(out, "out");
+  check_same(in, out, "in", "out");
+  AKV_CHECK(in.numel() == out.numel(), "in and out must have the same number of elements");
+  AKV_CHECK(kind >= 0 && kind <= 2, "activation: kind must be 0 (relu squared), 1 (tanh GELU) or 2 (SiLU)");
+  c10::cuda::CUDAGuard guard(in.device());
+  check_launch(akv::launch_activation(in.data_ptr(), out.data_ptr(), in.numel(), (int)kind, dtype_code(in, "in"),
+                                      stream_of(in)),
+               "activation");
+}
+
 int64_t sample_slices() { return akv::kSampleSlices; }
 
 // parts: float32 workspace of 4 * rows * slices entries (maxima, indices and, as doubles, sums); tickets: int32, at
@@ -752,6 +992,22 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("head_dim"), py::arg("rotary_dim"), py::arg("eps"), py::arg("status") = py::none());
   m.def("kv_write", &kv_write, py::arg("k"), py::arg("v"), py::arg("slots"), py::arg("k_cache"), py::arg("v_cache"),
         py::arg("status") = py::none());
+  m.def("scored_attention", &scored_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"),
+        py::arg("block_table"), py::arg("cu_q"), py::arg("ctx_lens"), py::arg("tile_seq"), py::arg("tile_q0"),
+        py::arg("tile_nq"), py::arg("partials"), py::arg("num_tiles"), py::arg("q_tile"), py::arg("num_splits"),
+        py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("v_dim"), py::arg("window"), py::arg("chunk"),
+        py::arg("scale"), py::arg("softcap"), py::arg("slopes") = py::none(), py::arg("gate") = py::none(),
+        py::arg("status") = py::none());
+  m.def("head_prep", &head_prep, py::arg("x"), py::arg("slots"), py::arg("q_out"), py::arg("k_cache"),
+        py::arg("v_cache"), py::arg("v_keep"), py::arg("v_other"), py::arg("blend_weight"), py::arg("gate_out"),
+        py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("v_dim"), py::arg("unit_norm"),
+        py::arg("eps"), py::arg("status") = py::none());
+  m.def("latent_prep", &latent_prep, py::arg("x"), py::arg("positions"), py::arg("slots"), py::arg("q_weight"),
+        py::arg("kv_weight"), py::arg("inv_freq"), py::arg("q_latent"), py::arg("cache"), py::arg("q_rank"),
+        py::arg("kv_rank"), py::arg("rot_dim"), py::arg("rotary_dims"), py::arg("eps"), py::arg("status") = py::none());
+  m.def("rotate_pairs", &rotate_pairs, py::arg("in"), py::arg("out"), py::arg("positions"), py::arg("inv_freq"),
+        py::arg("heads"), py::arg("cols"), py::arg("rotary_dims"), py::arg("in_offset"), py::arg("out_offset"));
+  m.def("activation", &activation, py::arg("in"), py::arg("out"), py::arg("kind"));
   m.def("paged_attention", &paged_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"),
         py::arg("block_table"), py::arg("cu_q"), py::arg("ctx_lens"), py::arg("tile_seq"), py::arg("tile_q0"),
         py::arg("tile_nq"), py::arg("partials"), py::arg("num_tiles"), py::arg("q_tile"), py::arg("num_splits"),

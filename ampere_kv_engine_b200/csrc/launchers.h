@@ -186,6 +186,76 @@ bool attention_tc_merges_in_kernel(const PagedAttentionParams& p);
 bool attention_tcgen05_supported(const PagedAttentionParams& p);
 int launch_attention_tcgen05(const PagedAttentionParams& p, cudaStream_t stream);
 
+// Attention whose scores are reshaped before the softmax and whose keys and values may differ in width
+// (scored_attention.cu).  `base` is read as for launch_paged_attention with these differences: head_dim is the width
+// of a query / key row, out is [N, NH * v_dim], partials hold v_dim + 2 floats per (row, split), `kernel` is ignored.
+struct ScoredAttentionParams {
+  PagedAttentionParams base;
+  int v_dim;                   // width of a value row and of a head's output
+  int64_t k_row_stride;        // elements between consecutive (page, kv head, offset) rows of the key storage
+  int64_t v_row_stride;        // the same for the value storage (which may be the key storage: a value that is a
+                               // prefix of its key row)
+  float softcap;               // > 0: score <- softcap * tanh(score / softcap)
+  const float* slopes;         // [NH] or null: score <- score - slopes[h] * (query position - key position)
+  int chunk;                   // > 0: a query sees only the keys of its own block of `chunk` positions
+  const float* gate;           // [N, NH] or null: a head's output is multiplied by its gate
+};
+int launch_scored_attention(const ScoredAttentionParams& p, cudaStream_t stream);
+
+// What stands between one product that holds [q heads | k heads | v heads | a gate column per q head] of every token
+// and the attention over them (mixer_prep.cu): q and k heads scaled to unit RMS, v blended with another layer's
+// values of the same token, k and v written to their cache slots, gates through a sigmoid.
+struct HeadPrepParams {
+  const void* x;               // [N, NH * D + NKV * D + NKV * DV (+ NH)]
+  const int32_t* slots;        // [N] page * page_size + offset, or -1: not written; may be null
+  void* q_out;                 // [N, NH * D]
+  void* k_cache;               // [num_pages, NKV, page_size, k_row_stride] or null
+  void* v_cache;               // [num_pages, NKV, page_size, v_row_stride] or null
+  void* v_keep;                // [N, NKV * DV] or null: receives this layer's own values before the blend
+  const void* v_other;         // [N, NKV * DV] or null: v <- (1 - w) v + w v_other
+  const float* blend_weight;   // one float on the device (read when v_other is given)
+  float* gate_out;             // [N, NH] or null: sigmoid of the gate columns (null: x has no gate columns)
+  int64_t num_tokens;
+  int num_heads, num_kv_heads, head_dim, v_dim, page_size;
+  int64_t num_pages, k_row_stride, v_row_stride;
+  int unit_norm;               // 1: q and k heads are divided by sqrt(mean(x^2) + eps)
+  float eps;
+  int dtype;
+  int* status;
+};
+int launch_head_prep(const HeadPrepParams& p, cudaStream_t stream);
+
+// What stands between one product that holds [query latent | key/value latent | rotated key part] of every token and
+// what comes next: RMS norm with a plain weight on each latent, rotary positions on neighbouring pairs of the first
+// rotary_dims dims of the rotated part; the normed key/value latent and the rotated part go side by side into the
+// token's cache row [kv_rank + rot_dim].
+struct LatentPrepParams {
+  const void* x;               // [N, q_rank + kv_rank + rot_dim]
+  const int32_t* positions;    // [N]
+  const int32_t* slots;        // [N] or null
+  const float* q_weight;       // [q_rank]
+  const float* kv_weight;      // [kv_rank]
+  const float* inv_freq;       // [rotary_dims / 2]
+  void* q_latent;              // [N, q_rank]
+  void* cache;                 // [num_pages, 1, page_size, row_stride] or null
+  int64_t num_tokens;
+  int q_rank, kv_rank, rot_dim, rotary_dims, page_size;
+  int64_t num_pages, row_stride;
+  float eps;
+  int dtype;
+  int* status;
+};
+int launch_latent_prep(const LatentPrepParams& p, cudaStream_t stream);
+
+// out[t, h, out_offset + c] = rotated in[t, h, in_offset + c] for c < cols: dims 2i and 2i + 1 turn by
+// positions[t] * inv_freq[i] while 2i + 1 < rotary_dims, the rest passes unchanged.
+int launch_rotate_pairs(const void* in, void* out, const int32_t* positions, const float* inv_freq,
+                        int64_t num_tokens, int heads, int cols, int rotary_dims, int64_t in_width, int in_offset,
+                        int64_t out_width, int out_offset, int dtype, cudaStream_t stream);
+
+enum Activation : int { kActReluSquared = 0, kActGeluTanh = 1, kActSilu = 2 };
+int launch_activation(const void* in, void* out, int64_t total, int kind, int dtype, cudaStream_t stream);
+
 // tokens[r] = argmax(logits[r]) where temperature[r] == 0, else the inverse-CDF draw of
 // softmax(logits[r] / temperature[r]) at uniform[r].
 // A row is cut into kSampleSlices slices, a block each.  Workspaces: part_max / part_arg / part_sum hold

@@ -1,0 +1,316 @@
+// Paged causal attention whose scores are reshaped before the softmax and whose keys and values
+// need not have the same width: the general kernel (float arithmetic on CUDA cores, float32 or
+// bfloat16 pages) for mixers that the plain kernel of paged_attention.cu does not describe.
+//
+//   score(i, j) = q_i . k_j * scale
+//   cap  > 0:     score <- cap * tanh(score / cap)
+//   slopes:       score <- score - slopes[h] * (i - j)            (a bias that grows with the distance)
+//   visible(i,j): j <= i, j > i - window (window > 0), floor(j / chunk) == floor(i / chunk) (chunk > 0)
+//   out_i = softmax over the visible j of score(i, j) applied to v_j, times gate[i, h] (if given)
+//
+// Keys are rows of `head_dim` elements, values rows of `v_dim`; both live in paged storage
+// [pages, kv heads, page size, row stride] whose row strides are given, so a value may be a
+// prefix of the key row it shares (a cache that keeps one compressed latent per token, read as
+// key and, in its first v_dim elements, as value).
+//
+// Work split, as in the plain general kernel: a warp owns (tile, kv head, R rows of the tile,
+// key split); rows are (token, head-in-group) pairs.  It walks its key range 32 keys at a time,
+// lane = key for the scores (the key row is read once for all R rows, q comes from shared
+// memory), lane = value dims for P.V.  With several splits the partial (acc, max, sum) go to a
+// workspace and a second kernel merges them in split order.
+#include "common.cuh"
+#include "launchers.h"
+
+#include <math_constants.h>
+
+namespace akv {
+
+constexpr int kScoredWarps = 4;
+
+template <typename T, int DC, int R>
+__global__ void __launch_bounds__(kScoredWarps * 32)
+scored_attention_kernel(ScoredAttentionParams sp, int row_groups, int64_t total_items, int vec) {
+  const PagedAttentionParams& p = sp.base;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t item = (int64_t)blockIdx.x * kScoredWarps + warp;
+  if (item >= total_items) return;
+  const int D = p.head_dim, DV = sp.v_dim, NH = p.num_heads, NKV = p.num_kv_heads, G = NH / NKV, P = p.page_size;
+  const int rg = (int)(item % row_groups);
+  const int kvh = (int)((item / row_groups) % NKV);
+  const int split = (int)((item / ((int64_t)row_groups * NKV)) % p.num_splits);
+  const int tile = (int)(item / ((int64_t)row_groups * NKV * p.num_splits));
+
+  const int seq = p.tile_seq[tile];
+  const int q0 = p.tile_q0[tile];
+  const int nq = p.tile_nq[tile];
+  const int rows_in_tile = nq * G;
+  const int row0 = rg * R;
+  if (row0 >= rows_in_tile) return;
+  const int nrows = min(R, rows_in_tile - row0);
+  const int ctx = p.ctx_lens[seq];
+  const int seq_q0 = p.cu_q[seq];
+  const int q_len = p.cu_q[seq + 1] - seq_q0;
+  const int tile_pos = ctx - q_len + (q0 - seq_q0);      // absolute position of the tile's first token
+
+  extern __shared__ float smem[];
+  float* qs = smem + warp * (R * D + R * 32);
+  float* ps = qs + R * D;
+
+  const T* q = (const T*)p.q;
+  for (int idx = lane; idx < R * D; idx += 32) {
+    const int r = idx / D, d = idx - r * D;
+    float v = 0.f;
+    if (r < nrows) {
+      const int rr = row0 + r;
+      const int64_t token = q0 + rr / G;
+      const int head = kvh * G + rr % G;
+      v = to_float<T>(q[(token * NH + head) * (int64_t)D + d]) * p.scale;
+    }
+    qs[idx] = v;
+  }
+  __syncwarp();
+
+  int pos[R], first_key[R];
+  float slope[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const bool live = r < nrows;
+    pos[r] = live ? tile_pos + (row0 + r) / G : -1;
+    int first = 0;
+    if (live && p.window > 0) first = max(first, pos[r] - p.window + 1);
+    if (live && sp.chunk > 0) first = max(first, pos[r] / sp.chunk * sp.chunk);
+    first_key[r] = first;
+    slope[r] = (live && sp.slopes != nullptr) ? sp.slopes[kvh * G + (row0 + r) % G] : 0.f;
+  }
+  const int pos_last = tile_pos + (row0 + nrows - 1) / G;
+  const int lo_item = first_key[0];        // rows are in position order: the first row's first key is the lowest
+  const int hi_item = pos_last + 1;
+  int per = (max(hi_item - lo_item, 0) + p.num_splits - 1) / p.num_splits;
+  per = (per + 31) & ~31;
+  const int start = lo_item + split * per;
+  const int end = min(hi_item, start + per);
+  const float inv_cap = sp.softcap > 0.f ? 1.f / sp.softcap : 0.f;
+
+  float m[R], l[R], acc[R][DC];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    m[r] = -CUDART_INF_F;
+    l[r] = 0.f;
+#pragma unroll
+    for (int c = 0; c < DC; ++c) acc[r][c] = 0.f;
+  }
+
+  const T* k_cache = (const T*)p.k_cache;
+  const T* v_cache = (const T*)p.v_cache;
+  const int32_t* table = p.block_table + (int64_t)seq * p.table_width;
+
+  for (int kb = start; kb < end; kb += 32) {
+    const int key = kb + lane;
+    bool kvalid = key < end;
+    int page = 0;
+    if (kvalid) {
+      const int logical = key / P;
+      page = logical < p.table_width ? table[logical] : -1;
+      if (page < 0 || page >= p.num_pages) {
+        set_status(p.status, kBadPage);
+        kvalid = false;
+        page = 0;
+      }
+    }
+    const int off = key % P;
+    float s[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) s[r] = 0.f;
+    if (kvalid) {
+      const T* kptr = k_cache + (((int64_t)page * NKV + kvh) * P + off) * sp.k_row_stride;
+      if (vec) {
+#pragma unroll 2
+        for (int d0 = 0; d0 < D; d0 += 8) {
+          float kf[8];
+          load8<T>(kptr + d0, kf);
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const float4 a = *reinterpret_cast<const float4*>(qs + r * D + d0);
+            const float4 b = *reinterpret_cast<const float4*>(qs + r * D + d0 + 4);
+            s[r] += a.x * kf[0] + a.y * kf[1] + a.z * kf[2] + a.w * kf[3] + b.x * kf[4] + b.y * kf[5] +
+                    b.z * kf[6] + b.w * kf[7];
+          }
+        }
+      } else {
+        for (int d = 0; d < D; ++d) {
+          const float kf = to_float<T>(kptr[d]);
+#pragma unroll
+          for (int r = 0; r < R; ++r) s[r] += qs[r * D + d] * kf;
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const bool visible = kvalid && key <= pos[r] && key >= first_key[r];
+      float sr = s[r];
+      if (sp.softcap > 0.f) sr = sp.softcap * tanhf(sr * inv_cap);
+      sr -= slope[r] * (float)(pos[r] - key);
+      sr = visible ? sr : -CUDART_INF_F;
+      const float m_new = fmaxf(m[r], warp_max(sr));
+      const float alpha = (m_new == -CUDART_INF_F) ? 1.f : expf(m[r] - m_new);
+      const float pr = visible ? expf(sr - m_new) : 0.f;
+      l[r] = l[r] * alpha + pr;
+      m[r] = m_new;
+#pragma unroll
+      for (int c = 0; c < DC; ++c) acc[r][c] *= alpha;
+      ps[r * 32 + lane] = pr;
+    }
+    __syncwarp();
+    const int nk = min(32, end - kb);
+    for (int j = 0; j < nk; ++j) {
+      const int pj = __shfl_sync(0xffffffffu, page, j);
+      const int offj = (kb + j) % P;
+      const T* vptr = v_cache + (((int64_t)pj * NKV + kvh) * P + offj) * sp.v_row_stride;
+      float vv[DC];
+#pragma unroll
+      for (int c = 0; c < DC; ++c) {
+        const int d = c * 32 + lane;
+        vv[c] = d < DV ? to_float<T>(vptr[d]) : 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float pr = ps[r * 32 + j];
+#pragma unroll
+        for (int c = 0; c < DC; ++c) acc[r][c] += pr * vv[c];
+      }
+    }
+    __syncwarp();
+  }
+
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    if (r >= nrows) continue;
+    const float total = warp_sum(l[r]);
+    const int rr = row0 + r;
+    const int64_t token = q0 + rr / G;
+    const int head = kvh * G + rr % G;
+    const int64_t row = token * NH + head;
+    if (p.num_splits == 1) {
+      T* o = (T*)p.out + row * (int64_t)DV;
+      float inv = total > 0.f ? 1.f / total : 0.f;
+      if (sp.gate != nullptr) inv *= sp.gate[row];
+#pragma unroll
+      for (int c = 0; c < DC; ++c) {
+        const int d = c * 32 + lane;
+        if (d < DV) o[d] = from_float<T>(acc[r][c] * inv);
+      }
+    } else {
+      float* part = p.partials + (row * p.num_splits + split) * (int64_t)(DV + 2);
+#pragma unroll
+      for (int c = 0; c < DC; ++c) {
+        const int d = c * 32 + lane;
+        if (d < DV) part[d] = acc[r][c];
+      }
+      if (lane == 0) {
+        part[DV] = m[r];
+        part[DV + 1] = total;
+      }
+    }
+  }
+}
+
+// out[row] = gate[row] * sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s, splits taken in order; one block per
+// (tile, row of the tile, q-head), so only the rows of the call's tiles are written.
+template <typename T>
+__global__ void scored_merge_kernel(const float* __restrict__ partials, T* __restrict__ out,
+                                    const int32_t* __restrict__ tile_q0, const int32_t* __restrict__ tile_nq,
+                                    const float* __restrict__ gate, int q_tile, int num_heads, int num_splits,
+                                    int v_dim) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t per_tile = (int64_t)q_tile * num_heads;
+  const int64_t tile = blockIdx.x / per_tile;
+  const int in_tile = (int)(blockIdx.x - tile * per_tile);
+  const int r = in_tile / num_heads, head = in_tile - r * num_heads;
+  if (r >= tile_nq[tile]) return;
+  const int64_t row = ((int64_t)tile_q0[tile] + r) * num_heads + head;
+  const float* base = partials + row * num_splits * (int64_t)(v_dim + 2);
+  float m = -CUDART_INF_F;
+  for (int s = 0; s < num_splits; ++s) {
+    const float* part = base + (int64_t)s * (v_dim + 2);
+    if (part[v_dim + 1] > 0.f) m = fmaxf(m, part[v_dim]);
+  }
+  const float g = gate != nullptr ? gate[row] : 1.f;
+  for (int d = threadIdx.x; d < v_dim; d += blockDim.x) {
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float* part = base + (int64_t)s * (v_dim + 2);
+      const float ls = part[v_dim + 1];
+      if (ls > 0.f) {
+        const float w = expf(part[v_dim] - m);
+        num += w * part[d];
+        den += w * ls;
+      }
+    }
+    out[row * v_dim + d] = from_float<T>(den > 0.f ? g * num / den : 0.f);
+  }
+}
+
+template <typename T, int DC, int R>
+static int launch_rows(const ScoredAttentionParams& sp, cudaStream_t stream) {
+  const PagedAttentionParams& p = sp.base;
+  const int G = p.num_heads / p.num_kv_heads;
+  const int row_groups = (p.q_tile * G + R - 1) / R;
+  const int64_t total = (int64_t)p.num_tiles * p.num_kv_heads * row_groups * p.num_splits;
+  const int64_t blocks = (total + kScoredWarps - 1) / kScoredWarps;
+  if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)kScoredWarps * (R * p.head_dim + R * 32) * sizeof(float);
+  auto kernel = scored_attention_kernel<T, DC, R>;
+  if (smem > 48 * 1024) {
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+  }
+  // 16-byte loads of the key rows and of q in shared memory need rows that start on such a boundary
+  const int per16 = 16 / (int)sizeof(T);
+  const int vec = (p.head_dim % 8 == 0 && sp.k_row_stride % per16 == 0 &&
+                   reinterpret_cast<uintptr_t>(p.k_cache) % 16 == 0) ? 1 : 0;
+  kernel<<<(unsigned)blocks, kScoredWarps * 32, smem, stream>>>(sp, row_groups, total, vec);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return (int)err;
+  if (p.num_splits > 1) {
+    const int64_t merge_blocks = (int64_t)p.num_tiles * p.q_tile * p.num_heads;
+    if (merge_blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+    const int threads = sp.v_dim <= 32 ? 32 : (sp.v_dim <= 64 ? 64 : 128);
+    scored_merge_kernel<T><<<(unsigned)merge_blocks, threads, 0, stream>>>(
+        p.partials, (T*)p.out, p.tile_q0, p.tile_nq, sp.gate, p.q_tile, p.num_heads, p.num_splits, sp.v_dim);
+    return (int)cudaGetLastError();
+  }
+  return 0;
+}
+
+template <typename T>
+static int launch_scored_typed(const ScoredAttentionParams& sp, cudaStream_t stream) {
+  const int dc = (sp.v_dim + 31) / 32;
+#define AKV_SCORED(DCV, RV) \
+  case DCV: return launch_rows<T, DCV, RV>(sp, stream);
+  switch (dc) {
+    AKV_SCORED(1, 8) AKV_SCORED(2, 8) AKV_SCORED(3, 8) AKV_SCORED(4, 8)
+    AKV_SCORED(5, 8) AKV_SCORED(6, 8) AKV_SCORED(7, 8) AKV_SCORED(8, 8)
+    default: break;
+  }
+#undef AKV_SCORED
+  // wide values (a compressed latent read as value): fewer rows per warp keep the accumulators in registers
+  if (dc <= 12) return launch_rows<T, 12, 4>(sp, stream);
+  if (dc <= 16) return launch_rows<T, 16, 4>(sp, stream);
+  return (int)cudaErrorInvalidValue;
+}
+
+int launch_scored_attention(const ScoredAttentionParams& sp, cudaStream_t stream) {
+  const PagedAttentionParams& p = sp.base;
+  if (p.num_tiles == 0 || p.num_tokens == 0) return 0;
+  if (p.head_dim < 1 || sp.v_dim < 1 || sp.v_dim > 512 || p.num_heads % p.num_kv_heads || p.num_splits < 1 ||
+      sp.k_row_stride < p.head_dim || sp.v_row_stride < sp.v_dim || sp.chunk < 0 || sp.softcap < 0.f)
+    return (int)cudaErrorInvalidValue;
+  return p.dtype == kBFloat16 ? launch_scored_typed<__nv_bfloat16>(sp, stream)
+                              : launch_scored_typed<float>(sp, stream);
+}
+
+}  // namespace akv

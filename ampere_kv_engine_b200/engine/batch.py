@@ -72,6 +72,9 @@ class StepContext:
     ctx_lens_host: list[int] = field(default_factory=list)
     state_slots_host: list[int] = field(default_factory=list)
     h2d_bytes: int = 0              # size of the one host-to-device copy that carried all of the above
+    #: what one layer leaves for later layers of the same step, by name (values that a later mixer blends with its
+    #: own, for instance); emptied when a step's forward pass begins
+    shared: dict = field(default_factory=dict)
 
 
 def _align(n: int, to: int = 4) -> int:

@@ -243,7 +243,7 @@ class Scheduler:
         page = self.manager.page_size
         conservative = (total_tokens + page) // page
         bounds = self.manager.pages_for_tokens(total_tokens, self.max_batch_tokens)
-        return [min(conservative, b + 1) if g.window is not None else conservative
+        return [min(conservative, b + 1) if (g.window is not None or g.chunk is not None) else conservative
                 for g, b in zip(self.manager.groups, bounds)]
 
     def _live(self) -> list[Request]:

@@ -252,6 +252,73 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, 
     return out
 
 
+def scored_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq, *, num_tiles,
+                     q_tile, num_splits, num_heads, num_kv_heads, v_dim, scale, window=0, chunk=0, softcap=0.0,
+                     slopes=None, gate=None, partials=None, status=None, out=None):
+    """Causal attention of the batch's new tokens over paged keys and values of different widths, with the score
+    reshaped before the softmax: ``softcap * tanh(score / softcap)`` (``softcap`` > 0), less ``slopes[h]`` times the
+    distance to the key (``slopes`` float32 [heads]); a query sees the last ``window`` keys (``window`` > 0) of its own
+    block of ``chunk`` positions (``chunk`` > 0); ``gate`` (float32 [tokens, heads]) scales each head's output.
+    ``k_cache`` / ``v_cache``: [pages, kv heads, page size, width]; they may be one tensor whose rows are read whole
+    as keys and in their first ``v_dim`` elements as values.  Returns [tokens, heads * v_dim]; only the rows of the
+    given tiles are written."""
+    if out is None:
+        out = torch.empty((q.shape[0], num_heads * v_dim), dtype=q.dtype, device=q.device)
+    if num_splits > 1 and partials is None:
+        partials = torch.empty((q.shape[0] * num_heads * num_splits * (v_dim + 2),), dtype=torch.float32,
+                               device=q.device)
+    ext().scored_attention(q, k_cache, v_cache, out, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq, partials,
+                           num_tiles, q_tile, num_splits, num_heads, num_kv_heads, int(v_dim), int(window or 0),
+                           int(chunk or 0), float(scale), float(softcap or 0.0), slopes, gate, status)
+    _launched(2 if num_splits > 1 else 1)
+    return out
+
+
+def head_prep(x, slots, k_cache, v_cache, *, num_heads, num_kv_heads, head_dim, v_dim, unit_norm, eps, gated,
+              v_keep=None, v_other=None, blend_weight=None, status=None):
+    """From one product ``x`` [tokens, q heads | k heads | v heads | a gate column per q head]: q (and k) heads
+    scaled to unit RMS, ``v <- (1 - blend_weight) v + blend_weight v_other``, k and v written to their cache slots;
+    ``v_keep`` receives the layer's own values before the blend.  Returns (q [tokens, heads * head_dim], sigmoid of
+    the gate columns as float32 [tokens, heads], or None without ``gated``)."""
+    n = x.shape[0]
+    q_out = torch.empty((n, num_heads * head_dim), dtype=x.dtype, device=x.device)
+    gate = torch.empty((n, num_heads), dtype=torch.float32, device=x.device) if gated else None
+    ext().head_prep(x, slots, q_out, k_cache, v_cache, v_keep, v_other, blend_weight, gate, num_heads, num_kv_heads,
+                    head_dim, v_dim, bool(unit_norm), float(eps), status)
+    _launched()
+    return q_out, gate
+
+
+def latent_prep(x, positions, slots, q_weight, kv_weight, inv_freq, cache, *, q_rank, kv_rank, rot_dim, rotary_dims,
+                eps, status=None):
+    """From one product ``x`` [tokens, query latent | key/value latent | rotated key part]: both latents through an
+    RMS norm with a plain weight, neighbouring pairs of the rotated part turned by position; the key/value latent
+    and the rotated part land side by side in the token's row of ``cache``.  Returns the query latent."""
+    q_latent = torch.empty((x.shape[0], q_rank), dtype=x.dtype, device=x.device)
+    ext().latent_prep(x, positions, slots, q_weight, kv_weight, inv_freq, q_latent, cache, q_rank, kv_rank, rot_dim,
+                      rotary_dims, float(eps), status)
+    _launched()
+    return q_latent
+
+
+def rotate_pairs(x, out, positions, inv_freq, *, heads, cols, rotary_dims, in_offset, out_offset) -> None:
+    """``out[t, h, out_offset + c] = x[t, h, in_offset + c]`` for ``c < cols``, dims 2i and 2i + 1 of the range
+    turned by ``positions[t] * inv_freq[i]`` while they lie in the first ``rotary_dims``."""
+    ext().rotate_pairs(x, out, positions, inv_freq, heads, cols, rotary_dims, in_offset, out_offset)
+    _launched()
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """``relu(x) ** 2`` (``"relu2"``), the tanh form of GELU (``"gelu_tanh"``) or SiLU, element by element."""
+    out = torch.empty_like(x)
+    ext().activation(x, out, ACTIVATIONS[kind])
+    _launched()
+    return out
+
+
 _SAMPLE_TICKETS: dict = {}      # per device: zeroed row counters of the sampling kernel (it leaves them zero)
 
 

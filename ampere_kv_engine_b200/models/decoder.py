@@ -13,7 +13,8 @@ import torch
 
 from ..config.spec import ModelSpec
 from ..kernels import ops
-from ..parts import attention, block, embedding, feed_forward, norm, position  # noqa: F401  (register the built-in kinds)
+from ..parts import (attention, block, embedding, feed_forward, latent_attention, norm, position,  # noqa: F401
+                     scored_attention)                          # (importing them registers the built-in kinds)
 from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, Block, CacheSpec, ParamSpec, build_part
 
 
@@ -97,6 +98,8 @@ class DecoderModel:
     def forward(self, ctx, cache_views) -> torch.Tensor | None:
         """Run the step's tokens through the schedule; logits [wanted, vocab] float32, or None if none wanted."""
         ops.stream_begin_step(self.device)
+        if getattr(ctx, "shared", None):
+            ctx.shared.clear()
         hidden = self.embedding.forward(ctx.token_ids, ctx)
         delta = None
         for pos, entry in enumerate(self.spec.schedule):

@@ -29,8 +29,11 @@ def register_architecture(name: str, config_class, build_spec) -> Architecture:
 
 def architecture_of(raw_config: dict) -> Architecture:
     names = raw_config.get("architectures")
+    if names is None and isinstance(raw_config.get("architecture"), str):
+        names = [raw_config["architecture"]]        # a config.json that names its one architecture in the singular
     if not names or not isinstance(names, (list, tuple)) or not isinstance(names[0], str):
-        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names "
+                          "(or 'architecture' one name)")
     if names[0] not in ARCHITECTURES:
         raise ConfigError(f"config.json: architecture {names[0]!r} is not registered; known: {sorted(ARCHITECTURES)}")
     return ARCHITECTURES[names[0]]
@@ -38,13 +41,13 @@ def architecture_of(raw_config: dict) -> Architecture:
 
 def load_config(model_dir: str):
     """(architecture, typed config) of a model folder."""
-    from . import qwen3  # noqa: F401  (registers the built-in architecture)
+    from . import qwen3, sukalorn  # noqa: F401  (registers the built-in architectures)
     raw = read_config_json(model_dir)
     arch = architecture_of(raw)
     return arch, arch.config_class.from_dict(raw)
 
 
 def config_from_dict(raw: dict):
-    from . import qwen3  # noqa: F401
+    from . import qwen3, sukalorn  # noqa: F401
     arch = architecture_of(raw)
     return arch, arch.config_class.from_dict(raw)

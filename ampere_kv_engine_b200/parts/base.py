@@ -33,7 +33,8 @@ class ParamSpec:
 
     shape: tuple[int, ...]
     kind: str = "matrix"
-    init: str = "normal"        # "normal": N(0, 0.02); "norm": 1 + N(0, 0.1); "zeros"
+    #: "normal": N(0, 0.02); "norm": 1 + N(0, 0.1); "around_zero": N(0, 0.1); "unit_interval": U(0, 1); "zeros"
+    init: str = "normal"
     optional: bool = False
 
 
@@ -50,8 +51,10 @@ class CacheTensor:
 class CacheSpec:
     """What a mixer needs the cache manager to keep for each request.
 
-    ``kind``: ``"none"``, ``"full"`` (every position is kept) or ``"window"`` (only the last
-    ``window`` positions are ever read, pages behind it are given back).  What a position stores
+    ``kind``: ``"none"``, ``"full"`` (every position is kept), ``"window"`` (only the last
+    ``window`` positions are ever read, pages behind it are given back) or ``"chunk"`` (a position reads only
+    positions of its own block of ``chunk`` positions, counted from the start of the sequence; pages wholly before
+    the block of the next position are given back).  What a position stores
     is a tuple of named tensors (``tensors``); when none is given it is what attention stores:
     ``k`` and ``v``, each ``num_kv_heads`` rows of ``head_dim``.  A mixer that keeps one
     compressed tensor per token, or keys and values of different widths, names them itself.
@@ -66,6 +69,7 @@ class CacheSpec:
     window: int | None = None
     state_shape: tuple[int, ...] = ()
     tensors: tuple[CacheTensor, ...] | None = None
+    chunk: int | None = None
 
     def stored(self) -> tuple[CacheTensor, ...]:
         if self.kind == "none":
@@ -75,7 +79,7 @@ class CacheSpec:
         return (CacheTensor("k", self.num_kv_heads, self.head_dim), CacheTensor("v", self.num_kv_heads, self.head_dim))
 
     def group_key(self) -> tuple:
-        return (self.kind, self.stored(), self.window)
+        return (self.kind, self.stored(), self.window, self.chunk)
 
 
 class Part:

@@ -14,17 +14,22 @@ from .base import Block, register_block
 
 @register_block("prenorm")
 class PreNormBlock(Block):
-    """roles: ``mixer_norm``, ``mixer``, ``feed_forward_norm``, ``feed_forward``."""
+    """roles: ``mixer_norm``, ``mixer``, ``feed_forward_norm``, ``feed_forward``.  A layer spec without a
+    feed-forward makes a layer of the mixer branch alone."""
 
     def __init__(self, layer, **kw):
         super().__init__(layer, **kw)
         self.mixer_norm = self.build_role("mixer_norm")
         self.mixer = self.build_role("mixer")
-        self.feed_forward_norm = self.build_role("feed_forward_norm")
-        self.feed_forward = self.build_role("feed_forward")
+        self.feed_forward = self.feed_forward_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = self.build_role("feed_forward_norm")
+            self.feed_forward = self.build_role("feed_forward")
 
     def forward(self, hidden, delta, ctx, cache):
         x = self.run_norm(self.mixer_norm, hidden, delta, ctx, consumer=self.mixer)
         attn = self.run_branch(self.mixer, hidden, x, ctx, cache)
+        if self.feed_forward is None:
+            return hidden, attn
         x = self.run_norm(self.feed_forward_norm, hidden, attn, ctx, consumer=self.feed_forward)
         return hidden, self.run_branch(self.feed_forward, hidden, x, ctx)

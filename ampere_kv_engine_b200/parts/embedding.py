@@ -10,12 +10,12 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import Embedding, Head, ParamSpec, register_embedding, register_head
+from .base import NORMS, Embedding, Head, ParamSpec, build_part, register_embedding, register_head
 
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Embedding):
-    """params: ``vocab_size``."""
+    """params: ``vocab_size``, ``tensor`` (the matrix's name under the prefix, default ``weight``)."""
 
     graph_safe = True
 
@@ -23,22 +23,43 @@ class TokenEmbedding(Embedding):
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)
         self.vocab_size = int(spec.params["vocab_size"])
+        self.tensor = str(spec.params.get("tensor", "weight"))
         self.weight: torch.Tensor | None = None
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.vocab_size, self.hidden_size))}
+        return {self.tensor: ParamSpec((self.vocab_size, self.hidden_size))}
 
     def load(self, tensors):
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.tensor].contiguous()
 
     def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
         return ops.embedding(token_ids, self.weight, status=getattr(ctx, "status", None),
                              sampled=getattr(ctx, "sampled", None))
 
 
+@register_embedding("normed_token_embedding")
+class NormedTokenEmbedding(TokenEmbedding):
+    """A row gather followed by a norm: the residual stream starts as the normed row.  params: those of
+    ``token_embedding`` and ``norm`` (a PartSpec of a registered norm kind)."""
+
+    def __init__(self, spec, **kw):
+        super().__init__(spec, **kw)
+        self.norm = build_part(NORMS, spec.params["norm"], hidden_size=self.hidden_size, dtype=torch.float32,
+                               device=self.device)
+
+    def children(self):
+        return (self.norm,)
+
+    def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
+        rows = super().forward(token_ids, ctx)
+        # the norm part, asked for float32 activations, hands back the stream itself
+        return self.norm.forward(rows, None, ctx)
+
+
 @register_head("linear_head")
 class LinearHead(Head):
-    """params: ``vocab_size``, ``tied`` (read the embedding's matrix instead of one's own).  A tied checkpoint may
+    """params: ``vocab_size``, ``tied`` (read the embedding's matrix instead of one's own), ``tensor`` (the
+    matrix's name under the prefix, default ``weight``).  A tied checkpoint may
     still carry the head's tensor: it is accepted if it equals the embedding's and refused if it differs."""
 
     graph_safe = True
@@ -48,16 +69,17 @@ class LinearHead(Head):
         super().__init__(spec, **kw)
         self.vocab_size = int(spec.params["vocab_size"])
         self.tied = bool(spec.params.get("tied", False))
+        self.tensor = str(spec.params.get("tensor", "weight"))
         self.weight: torch.Tensor | None = None
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.vocab_size, self.hidden_size), optional=self.tied)}
+        return {self.tensor: ParamSpec((self.vocab_size, self.hidden_size), optional=self.tied)}
 
     def load(self, tensors):
         if not self.tied:
-            self.weight = tensors["weight"].contiguous()
+            self.weight = tensors[self.tensor].contiguous()
         else:
-            self._stored = tensors.get("weight")
+            self._stored = tensors.get(self.tensor)
 
     def tie(self, embedding) -> None:
         if not self.tied:
@@ -68,7 +90,7 @@ class LinearHead(Head):
         stored = getattr(self, "_stored", None)
         if stored is not None and not torch.equal(stored, embedding.weight):
             from ..weights.loader import WeightError
-            name = f"{self.spec.prefix}.weight" if self.spec.prefix else "weight"
+            name = f"{self.spec.prefix}.{self.tensor}" if self.spec.prefix else self.tensor
             raise WeightError(f"the checkpoint ties the head to the embedding but carries a different {name} "
                               f"(largest difference {float((stored.float() - embedding.weight.float()).abs().max()):.3g})")
         self._stored = None

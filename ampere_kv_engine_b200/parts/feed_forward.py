@@ -70,3 +70,42 @@ class GatedMLP(FeedForward):
             if summed is not None:
                 return summed
         return ops.linear(act, self.down, partial_ok=True, status=status)
+
+
+@register_feed_forward("dense_mlp")
+class DenseMLP(FeedForward):
+    """``down(act(up(x)))`` without a gate.  params: ``intermediate_size``, ``activation`` (``"relu2"``: the square
+    of relu; ``"gelu_tanh"``; ``"silu"``), ``up`` / ``down`` (the matrices' names under the prefix, defaults
+    ``up_proj.weight`` / ``down_proj.weight``)."""
+
+    graph_safe = True
+    takes_lazy_norm = True
+    adds_residual = True
+
+    def __init__(self, spec, **kw):
+        super().__init__(spec, **kw)
+        self.intermediate_size = int(spec.params["intermediate_size"])
+        self.activation = str(spec.params.get("activation", "relu2"))
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"dense_mlp: activation {self.activation!r} is not one of {sorted(ops.ACTIVATIONS)}")
+        self.up_name = str(spec.params.get("up", "up_proj.weight"))
+        self.down_name = str(spec.params.get("down", "down_proj.weight"))
+        self.up: torch.Tensor | None = None
+        self.down: torch.Tensor | None = None
+
+    def param_specs(self):
+        i, h = self.intermediate_size, self.hidden_size
+        return {self.up_name: ParamSpec((i, h)), self.down_name: ParamSpec((h, i))}
+
+    def load(self, tensors):
+        self.up = tensors[self.up_name].contiguous()
+        self.down = tensors[self.down_name].contiguous()
+
+    def forward(self, x, ctx, residual=None):
+        status = getattr(ctx, "status", None)
+        act = ops.activation(ops.linear(x, self.up, status=status), self.activation)
+        if residual is not None:
+            summed = ops.linear_into_residual(act, self.down, residual, status=status)
+            if summed is not None:
+                return summed
+        return ops.linear(act, self.down, partial_ok=True, status=status)

@@ -17,7 +17,8 @@ from .base import Norm, ParamSpec, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    """params: ``size`` (defaults to the hidden size), ``eps``."""
+    """params: ``size`` (defaults to the hidden size), ``eps``, ``tensor`` (the weight's name under the prefix,
+    default ``weight``), ``unit_offset`` (the stored weight w is kept around zero and stands for ``1 + w``)."""
 
     graph_safe = True
 
@@ -26,13 +27,16 @@ class RMSNorm(Norm):
         super().__init__(spec, **kw)
         self.size = int(spec.params.get("size", self.hidden_size))
         self.eps = float(spec.params["eps"])
+        self.tensor = str(spec.params.get("tensor", "weight"))
+        self.unit_offset = bool(spec.params.get("unit_offset", False))
         self.weight: torch.Tensor | None = None
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.size,), kind="vector", init="norm")}
+        return {self.tensor: ParamSpec((self.size,), kind="vector", init="around_zero" if self.unit_offset else "norm")}
 
     def load(self, tensors):
-        self.weight = tensors["weight"]
+        # the factor the kernels multiply by: the stored weight, or one more than it (formed once, in float32)
+        self.weight = tensors[self.tensor] + 1.0 if self.unit_offset else tensors[self.tensor]
 
     takes_summed = True
     takes_pending = True

@@ -130,7 +130,8 @@ def main(argv=None) -> int:
         def build(dtype, **options):
             return Engine.from_random(raw_config, args.random_seed, config=base_options.replace(
                 dtype=dtype, kv_dtype=None, **options))
-        vocab = int(raw_config["vocab_size"])
+        from .models.registry import config_from_dict
+        vocab = int(config_from_dict(raw_config)[1].vocab_size)
     else:
         from .models.registry import load_config
 

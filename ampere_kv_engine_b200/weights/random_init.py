@@ -25,6 +25,10 @@ def _draw(spec: ParamSpec, generator: torch.Generator, device) -> torch.Tensor:
     noise = torch.randn(spec.shape, generator=generator, dtype=torch.float32, device=device)
     if spec.init == "norm":
         return 1.0 + 0.1 * noise
+    if spec.init == "around_zero":
+        return 0.1 * noise
+    if spec.init == "unit_interval":
+        return torch.rand(spec.shape, generator=generator, dtype=torch.float32, device=device)
     if spec.init == "zeros":
         return torch.zeros_like(noise)
     return 0.02 * noise

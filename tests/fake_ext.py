@@ -130,3 +130,115 @@ class FakeExt:
             target = float(uniform[r]) * float(cdf[-1])
             tokens[r] = min(int(torch.searchsorted(cdf, torch.tensor(target, dtype=torch.float64), right=True)),
                             logits.shape[1] - 1)
+
+    # ------------------------------------------------------------------ mixers with reshaped scores / latents
+
+    def scored_attention(self, q, k_cache, v_cache, out, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq,
+                         partials, num_tiles, q_tile, num_splits, num_heads, num_kv_heads, v_dim, window, chunk, scale,
+                         softcap, slopes=None, gate=None, status=None):
+        page_size = k_cache.shape[2]
+        d = q.shape[1] // num_heads
+        group = num_heads // num_kv_heads
+        cu = cu_q.tolist()
+        seqs = sorted(set(tile_seq.tolist()[:num_tiles]))
+        lens = ctx_lens.tolist()
+        for s in seqs:
+            ctx = lens[s]
+            q0, q1 = cu[s], cu[s + 1]
+            n = q1 - q0
+            first_pos = ctx - n
+            pos = torch.arange(first_pos, ctx)[:, None]
+            lo = 0
+            if window:
+                lo = max(lo, first_pos - window + 1)
+            if chunk:
+                lo = max(lo, first_pos // chunk * chunk)
+            keys = torch.arange(lo, ctx)
+            pages = block_table[s].long()[keys // page_size]
+            assert (pages >= 0).all(), "attention would read a page that is not held"
+            k = k_cache[pages, :, keys % page_size][..., :d].float()
+            v = v_cache[pages, :, keys % page_size][..., :v_dim].float()
+            qs = q[q0:q1].float().view(n, num_heads, d)
+            scores = torch.einsum("thd,shd->hts", qs, k.repeat_interleave(group, dim=1)) * scale
+            if softcap:
+                scores = softcap * torch.tanh(scores / softcap)
+            if slopes is not None:
+                scores = scores - slopes.float()[:, None, None] * (pos - keys[None, :]).float()[None]
+            visible = keys[None, :] <= pos
+            if window:
+                visible &= keys[None, :] > pos - window
+            if chunk:
+                visible &= (keys[None, :] // chunk) == (pos // chunk)
+            scores = scores.masked_fill(~visible[None], -math.inf)
+            o = torch.einsum("hts,shd->thd", torch.softmax(scores, -1), v.repeat_interleave(group, dim=1))
+            if gate is not None:
+                o = o * gate[q0:q1].float()[:, :, None]
+            out[q0:q1] = o.reshape(n, -1).to(out.dtype)
+
+    def head_prep(self, x, slots, q_out, k_cache, v_cache, v_keep, v_other, blend_weight, gate_out, num_heads,
+                  num_kv_heads, head_dim, v_dim, unit_norm, eps, status=None):
+        n = x.shape[0]
+        xf = x.float()
+        a, b, c = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * v_dim
+        q, k, v = xf[:, :a].view(n, num_heads, head_dim), xf[:, a:a + b].view(n, num_kv_heads, head_dim), \
+            xf[:, a + b:a + b + c].view(n, num_kv_heads, v_dim)
+        if unit_norm:
+            q = q * torch.rsqrt(q.square().mean(-1, keepdim=True) + eps)
+            k = k * torch.rsqrt(k.square().mean(-1, keepdim=True) + eps)
+        q_out.copy_(q.reshape(n, -1).to(q_out.dtype))
+        if v_keep is not None:
+            v_keep.copy_(v.reshape(n, -1).to(v_keep.dtype))
+        if v_other is not None:
+            lam = blend_weight.float()
+            v = (1 - lam) * v + lam * v_other.float().view(n, num_kv_heads, v_dim)
+        if gate_out is not None:
+            gate_out.copy_(torch.sigmoid(xf[:, a + b + c:]))
+        if k_cache is not None and slots is not None:
+            page_size = k_cache.shape[2]
+            keep = slots >= 0
+            s = slots[keep].long()
+            k_cache[s // page_size, :, s % page_size] = k[keep].to(k_cache.dtype)
+            v_cache[s // page_size, :, s % page_size] = v[keep].to(v_cache.dtype)
+
+    @staticmethod
+    def _turn_pairs(t, positions, inv_freq, rotary_dims):
+        if rotary_dims == 0:
+            return t
+        ang = positions.float()[:, None] * inv_freq[None, :]
+        shape = [t.shape[0]] + [1] * (t.dim() - 2) + [rotary_dims // 2]
+        cos, sin = ang.cos().view(shape), ang.sin().view(shape)
+        out = t.clone()
+        u, v = t[..., 0:rotary_dims:2], t[..., 1:rotary_dims:2]
+        out[..., 0:rotary_dims:2] = u * cos - v * sin
+        out[..., 1:rotary_dims:2] = v * cos + u * sin
+        return out
+
+    def latent_prep(self, x, positions, slots, q_weight, kv_weight, inv_freq, q_latent, cache, q_rank, kv_rank,
+                    rot_dim, rotary_dims, eps, status=None):
+        xf = x.float()
+        a, b, r = xf[:, :q_rank], xf[:, q_rank:q_rank + kv_rank], xf[:, q_rank + kv_rank:]
+        q_latent.copy_((a * torch.rsqrt(a.square().mean(-1, keepdim=True) + eps) * q_weight).to(q_latent.dtype))
+        if cache is None or slots is None:
+            return
+        c = b * torch.rsqrt(b.square().mean(-1, keepdim=True) + eps) * kv_weight
+        row = torch.cat((c, self._turn_pairs(r, positions, inv_freq, rotary_dims)), dim=-1)
+        page_size = cache.shape[2]
+        keep = slots >= 0
+        s = slots[keep].long()
+        cache[s // page_size, 0, s % page_size, :row.shape[1]] = row[keep].to(cache.dtype)
+
+    def rotate_pairs(self, x, out, positions, inv_freq, heads, cols, rotary_dims, in_offset, out_offset):
+        n = x.shape[0]
+        part = x.view(n, heads, -1)[:, :, in_offset:in_offset + cols].float()
+        out.view(n, heads, -1)[:, :, out_offset:out_offset + cols] = \
+            self._turn_pairs(part, positions, inv_freq, rotary_dims).to(out.dtype)
+
+    def activation(self, x, out, kind):
+        z = x.float()
+        if kind == 0:
+            y = torch.relu(z).square()
+        elif kind == 1:
+            y = 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
+        else:
+            y = z / (1 + torch.exp(-z))
+        out.copy_(y.to(out.dtype))
