@@ -80,6 +80,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 struct TcParams {
   PagedAttentionParams p;
   int box_rows;     // rows of one TMA box = min(page_size, keys per stage)
+  // the scored form of the decode kernel (launch_attention_tc_scored): see ScoredAttentionParams
+  float softcap = 0.f;
+  const float* slopes = nullptr;
+  int chunk = 0;
+  const float* gate = nullptr;
 };
 
 // Byte offset of (key k, 16-byte chunk c of the head) inside one stage's K or V area.  The area is laid out
@@ -514,7 +519,7 @@ struct CoopSmem {
   static constexpr int kBytes = STAGES * kStage + kExchange + 2 * STAGES * 8 + kCoopWarps * 16 * 4 + 1024;
 };
 
-template <int D, int STAGES, bool CLUSTER, int kCoopWarps>
+template <int D, int STAGES, bool CLUSTER, int kCoopWarps, bool kScored = false>
 __global__ void __launch_bounds__((kCoopWarps + 1) * 32)
 attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                              TcParams tp) {
@@ -549,6 +554,8 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
   const int pos = ctx - q_len + (q0 - seq_q0);
 
   int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int first_key = (kScored && tp.chunk > 0) ? pos / tp.chunk * tp.chunk : 0;   // the token's block of positions
+  lo = max(lo, first_key);
   lo = lo / tp.box_rows * tp.box_rows;
   const int hi = pos + 1;
   int range_lo = lo, range_hi = hi;
@@ -621,6 +628,12 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
     }
     const float scale_log2 = p.scale * kLog2e;
     const bool live[2] = {row_a < G, row_b < G};
+    float slope[2] = {0.f, 0.f};
+    if (kScored && tp.slopes != nullptr) {
+      if (live[0]) slope[0] = tp.slopes[kvh * G + row_a];
+      if (live[1]) slope[1] = tp.slopes[kvh * G + row_b];
+    }
+    const float inv_cap = (kScored && tp.softcap > 0.f) ? 1.f / tp.softcap : 0.f;
 
     for (int b = 0; b < num_blocks; ++b) {
       const int s = b % STAGES;
@@ -659,8 +672,16 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
           const int in_block = (warp * NQ + j) * 8 + (lane & 3) * 2 + (e & 1);
           const int key = key0 + in_block;
           const bool visible = ok && live[r] && in_block < nvalid && key <= pos &&
-                               (p.window <= 0 || key > pos - p.window);
-          sc[j][e] = visible ? sc[j][e] * scale_log2 : -CUDART_INF_F;
+                               (p.window <= 0 || key > pos - p.window) && (!kScored || key >= first_key);
+          if (kScored) {
+            // through the cap (tanh x = 1 - 2 / (2^(2 x log2 e) + 1)), less the distance bias, into log2 units
+            float x = sc[j][e] * p.scale;
+            if (tp.softcap > 0.f) x = tp.softcap * (1.f - __fdividef(2.f, exp2f(x * inv_cap * (2.f * kLog2e)) + 1.f));
+            x = fmaf(-slope[r], (float)(pos - key), x);
+            sc[j][e] = visible ? x * kLog2e : -CUDART_INF_F;
+          } else {
+            sc[j][e] = visible ? sc[j][e] * scale_log2 : -CUDART_INF_F;
+          }
           bmax[r] = fmaxf(bmax[r], sc[j][e]);
         }
       }
@@ -761,6 +782,8 @@ attention_decode_coop_kernel(const __grid_constant__ CUtensorMap k_map, const __
           float total = 0.f;
 #pragma unroll
           for (int w = 0; w < kCoopWarps; ++w) total += lpart[w * 16 + row];     // fixed order
+          // a head's gate: every use of the row sum divides by it, so the sum over the gate gates the output
+          if (kScored && tp.gate != nullptr) total = total / tp.gate[(int64_t)q0 * NH + kvh * G + row];
           merge[row * kRow + D + 1] = total;
         }
       }
@@ -876,6 +899,24 @@ int launch_coop(const PagedAttentionParams& p, int box_rows, const CUtensorMap& 
   return (int)launch_chain(kernel, grid, dim3((kCoopWarps + 1) * 32), smem, stream, cluster, k_map, v_map, tp);
 }
 
+template <int D, int STAGES, bool CLUSTER, int kCoopWarps>
+int launch_coop_scored(const ScoredAttentionParams& sp, int box_rows, const CUtensorMap& k_map, const CUtensorMap& v_map,
+                       cudaStream_t stream) {
+  const PagedAttentionParams& p = sp.base;
+  auto kernel = attention_decode_coop_kernel<D, STAGES, CLUSTER, kCoopWarps, true>;
+  constexpr int smem = CoopSmem<D, STAGES, kCoopWarps>::kBytes;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  TcParams tp{p, box_rows, sp.softcap, sp.slopes, sp.chunk, sp.gate};
+  const dim3 grid((unsigned)p.num_tiles, (unsigned)p.num_kv_heads, (unsigned)p.num_splits);
+  const dim3 cluster(1, 1, CLUSTER ? (unsigned)p.num_splits : 1u);
+  return (int)launch_chain(kernel, grid, dim3((kCoopWarps + 1) * 32), smem, stream, cluster, k_map, v_map, tp);
+}
+
 // Shape of the decode kernel's CTAs: (TMA ring stages of 16 KB at head size 128, consumer warps).  Bandwidth comes
 // from CTAs per SM, and a cluster's CTAs must all fit at once: rings of 4 or more stages (64 KB and up) made the
 // batch-8 kernel 25 us instead of 15 us.  Three stages pay since the producer fetches the blocks of old keys
@@ -953,6 +994,40 @@ int launch_attention_tc(const PagedAttentionParams& p, cudaStream_t stream) {
   }
   if (p.head_dim == 128) return launch_prompt<128, 64, 3, 8, 1>(p, box_rows, k_map, v_map, stream);
   return launch_prompt<64, 64, 3, 8, 1>(p, box_rows, k_map, v_map, stream);
+}
+
+// The decode kernel's scored form: single-token tiles, bfloat16, keys and values of the same 64 or 128 dims in storage
+// of their own; 1, 2, 4 or 8 key splits (more than one: merged inside the kernel by the cluster).
+bool attention_tc_scored_supported(const ScoredAttentionParams& sp) {
+  const PagedAttentionParams& p = sp.base;
+  return p.q_tile == 1 && sp.v_dim == p.head_dim && sp.k_row_stride == p.head_dim && sp.v_row_stride == p.head_dim &&
+         p.k_cache != p.v_cache && (p.num_splits == 1 || attention_tc_merges_in_kernel(p)) && attention_tc_supported(p);
+}
+
+int launch_attention_tc_scored(const ScoredAttentionParams& sp, cudaStream_t stream) {
+  const PagedAttentionParams& p = sp.base;
+  const int box_rows = p.page_size < 32 ? p.page_size : 32;
+  const int64_t rows = p.num_pages * p.num_kv_heads * (int64_t)p.page_size;
+  CUtensorMap k_map, v_map;
+  if (!cache_map(p.k_cache, rows, p.head_dim, box_rows, &k_map) ||
+      !cache_map(p.v_cache, rows, p.head_dim, box_rows, &v_map))
+    return (int)cudaErrorInvalidValue;
+  const bool merge = p.num_splits > 1;
+  // a block of the token's own positions bounds the walk as a window does
+  int64_t bound_keys = (int64_t)p.table_width * p.page_size;
+  if (p.window > 0) bound_keys = p.window;
+  if (sp.chunk > 0 && sp.chunk < bound_keys) bound_keys = sp.chunk;
+  const bool two_warps = decode_config(p.num_splits, bound_keys / p.num_splits / 32) == 6;
+#define AKV_COOP_SCORED(D, W)                                                                   \
+  return merge ? launch_coop_scored<D, 3, true, W>(sp, box_rows, k_map, v_map, stream)           \
+               : launch_coop_scored<D, 3, false, W>(sp, box_rows, k_map, v_map, stream);
+  if (p.head_dim == 128) {
+    if (two_warps) { AKV_COOP_SCORED(128, 2) }
+    AKV_COOP_SCORED(128, 4)
+  }
+  if (two_warps) { AKV_COOP_SCORED(64, 2) }
+  AKV_COOP_SCORED(64, 4)
+#undef AKV_COOP_SCORED
 }
 
 }  // namespace akv

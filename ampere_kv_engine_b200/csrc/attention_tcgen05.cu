@@ -118,6 +118,14 @@ struct FaParams {
   int tq;          // tokens per CTA = 128 / G
   int subtiles;    // CTAs per batch tile
   int box_rows;    // rows of one K/V box = min(page_size, 64)
+  // the scored form of the narrow kernel (launch_attention_tcgen05_scored): the score q.k * scale goes through
+  // softcap * tanh(. / softcap) (softcap > 0), loses slopes[h] * (query position - key position) (slopes given), a
+  // query sees only keys of its own block of `chunk` positions (chunk > 0), and a head's output is multiplied by
+  // gate[token, head] (gate given)
+  float softcap = 0.f;
+  const float* slopes = nullptr;
+  int chunk = 0;
+  const float* gate = nullptr;
 };
 
 // Shared memory: Q [2 halves][128 rows][128 B] | K/V ring: per stage K [2][64][128 B], V [2][64][128 B] |
@@ -180,7 +188,7 @@ constexpr float kRescaleThreshold = 8.f;     // log2 units
 // kStagesKV = 2: 96 KB of shared memory and at most 168 registers, two CTAs per SM (each takes half of the SM's
 // tensor memory): one CTA's softmax fills the other's waits.  kStagesKV = 4: one CTA per SM with a deeper K/V ring,
 // for launches with fewer CTAs than SMs.
-template <int kStagesKV>
+template <int kStagesKV, bool kScored>
 __global__ void __launch_bounds__(192, kStagesKV <= 2 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                          const __grid_constant__ CUtensorMap v_map, FaParams fp) {
@@ -224,6 +232,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
   const int q_len = p.cu_q[seq + 1] - seq_q0;
   const int tile_pos = ctx - q_len + (q0 - seq_q0);
   int lo = p.window > 0 ? max(0, tile_pos - p.window + 1) : 0;
+  if (kScored && fp.chunk > 0) lo = max(lo, tile_pos / fp.chunk * fp.chunk);      // the first row's block of positions
   lo = lo / fp.box_rows * fp.box_rows;
   const int hi = tile_pos + nq;
   const int num_blocks = (hi - lo + kKeys - 1) / kKeys;
@@ -393,7 +402,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     const bool live = token_local < nq;
     const int pos = tile_pos + token_local;
     const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-    const float scale_log2 = p.scale * kLog2e;
+    // the scored form turns each score into its final value in log2 units as soon as it is loaded
+    const float scale_log2 = kScored ? 1.f : p.scale * kLog2e;
+    const float slope = (kScored && fp.slopes != nullptr) ? fp.slopes[kvh * G + head_local] : 0.f;
+    const int first_key = (kScored && fp.chunk > 0 && live) ? pos / fp.chunk * fp.chunk : 0;
     float m_ref = -CUDART_INF_F, l = 0.f;
 
     for (int b = 0; b < num_blocks; ++b) {
@@ -411,8 +423,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       // Unscaled scores stay where the load put them; masked keys become -inf.  Most blocks lie wholly below the
       // diagonal, inside the window and inside the sequence: no masks there.  The maximum is taken along four
       // independent chains (one chain of 64 dependent maxima was a quarter of the block's time).
+      if (kScored) {
+        // score * scale, through the cap (tanh x = 1 - 2 / (2^(2 x log2 e) + 1): an exponential and a division,
+        // relative error about 1e-6), less the distance bias, into log2 units
+        const float inv_cap = fp.softcap > 0.f ? 1.f / fp.softcap : 0.f;
+#pragma unroll
+        for (int j = 0; j < kKeys; ++j) {
+          float x = __uint_as_float(raw[j >> 5][j & 31]) * p.scale;
+          if (fp.softcap > 0.f)
+            x = fp.softcap * (1.f - __fdividef(2.f, ex2(x * inv_cap * (2.f * kLog2e)) + 1.f));
+          x = fmaf(-slope, (float)(pos - (key0 + j)), x);
+          raw[j >> 5][j & 31] = __float_as_uint(x * kLog2e);
+        }
+      }
       const bool plain = ok && nvalid == kKeys && key0 + kKeys - 1 <= tile_pos &&
-                         (p.window <= 0 || key0 > tile_pos + nq - 1 - p.window);
+                         (p.window <= 0 || key0 > tile_pos + nq - 1 - p.window) &&
+                         (!kScored || fp.chunk <= 0 || key0 >= (tile_pos + nq - 1) / fp.chunk * fp.chunk);
       float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
       if (plain && live) {
 #pragma unroll
@@ -421,7 +447,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
 #pragma unroll
         for (int j = 0; j < kKeys; ++j) {
           const int key = key0 + j;
-          const bool visible = ok && live && j < nvalid && key <= pos && (p.window <= 0 || key > pos - p.window);
+          const bool visible = ok && live && j < nvalid && key <= pos && (p.window <= 0 || key > pos - p.window) &&
+                               (!kScored || key >= first_key);
           if (!visible) raw[j >> 5][j & 31] = 0xff800000u;     // -inf
           mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[j >> 5][j & 31]));
         }
@@ -491,7 +518,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     // O / l: the products run in order, so the last one done means all are
     if (num_blocks > 0 && ok && !bar_wait(&pv_done[(num_blocks - 1) & 1], ((num_blocks - 1) >> 1) & 1)) ok = false;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const float inv = (ok && l > 0.f) ? 1.f / l : 0.f;
+    float inv = (ok && l > 0.f) ? 1.f / l : 0.f;
+    if (kScored && fp.gate != nullptr && live) inv *= fp.gate[(int64_t)(q0 + token_local) * NH + kvh * G + head_local];
     __nv_bfloat16* out = (__nv_bfloat16*)p.out + ((int64_t)(q0 + token_local) * NH + kvh * G + head_local) * kD;
 #pragma unroll
     for (int c = 0; c < kD / 32; ++c) {
@@ -949,10 +977,10 @@ bool attention_tcgen05_supported(const PagedAttentionParams& p) {
 }
 
 namespace {
-template <int kStagesKV>
+template <int kStagesKV, bool kScored = false>
 int launch_stages(const CUtensorMap& q_map, const CUtensorMap& k_map, const CUtensorMap& v_map, const FaParams& fp,
                   dim3 grid, cudaStream_t stream) {
-  auto kernel = attention_tcgen05_kernel<kStagesKV>;
+  auto kernel = attention_tcgen05_kernel<kStagesKV, kScored>;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1017,6 +1045,31 @@ int launch_attention_tcgen05(const PagedAttentionParams& p, cudaStream_t stream)
   const bool shallow = forced ? forced == 2 : !few;
   if (shallow) return launch_stages<2>(q_map, k_map, v_map, fp, grid, stream);
   return launch_stages<4>(q_map, k_map, v_map, fp, grid, stream);
+}
+
+// The scored form: keys and values of 128 dims in storage of their own, everything else as the plain kernel takes it.
+bool attention_tcgen05_scored_supported(const ScoredAttentionParams& sp) {
+  return sp.v_dim == kD && sp.k_row_stride == kD && sp.v_row_stride == kD && sp.base.k_cache != sp.base.v_cache &&
+         attention_tcgen05_supported(sp.base);
+}
+
+int launch_attention_tcgen05_scored(const ScoredAttentionParams& sp, cudaStream_t stream) {
+  const PagedAttentionParams& p = sp.base;
+  const int G = p.num_heads / p.num_kv_heads;
+  const int tq = kRows / G;
+  const int subtiles = (p.q_tile + tq - 1) / tq;
+  const int box_rows = p.page_size < kKeys ? p.page_size : kKeys;
+  const int64_t rows = p.num_pages * p.num_kv_heads * (int64_t)p.page_size;
+  CUtensorMap q_map, k_map, v_map;
+  if (!q_map_for(p.q, p.num_tokens, p.num_heads, G, tq, &q_map) || !cache_map(p.k_cache, rows, box_rows, &k_map) ||
+      !cache_map(p.v_cache, rows, box_rows, &v_map))
+    return (int)cudaErrorInvalidValue;
+  FaParams fp{p, tq, subtiles, box_rows, sp.softcap, sp.slopes, sp.chunk, sp.gate};
+  fp.p.num_splits = 1;
+  const dim3 grid((unsigned)(p.num_tiles * subtiles), (unsigned)p.num_kv_heads, 1u);
+  // two CTAs per SM with two K/V stages each when there are more CTAs than SMs, else one with four stages
+  if ((int64_t)grid.x * grid.y > sm_count()) return launch_stages<2, true>(q_map, k_map, v_map, fp, grid, stream);
+  return launch_stages<4, true>(q_map, k_map, v_map, fp, grid, stream);
 }
 
 }  // namespace akv

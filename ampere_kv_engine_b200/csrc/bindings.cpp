@@ -703,7 +703,7 @@ void scored_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
                       const Tensor& tile_q0, const Tensor& tile_nq, const OptTensor& partials, int64_t num_tiles,
                       int64_t q_tile, int64_t num_splits, int64_t num_heads, int64_t num_kv_heads, int64_t v_dim,
                       int64_t window, int64_t chunk, double scale, double softcap, const OptTensor& slopes,
-                      const OptTensor& gate, const OptTensor& status) {
+                      const OptTensor& gate, const OptTensor& status, int64_t kernel) {
   check_cuda(q, "q");
   check_cuda(out, "out");
   check_same(q, out, "q", "out");
@@ -768,7 +768,7 @@ void scored_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   p.page_size = (int)k_cache.size(2);
   p.num_pages = k_cache.size(0);
   p.window = (int)window;
-  p.kernel = 1;
+  p.kernel = (int)kernel;          // 0: the best kernel that takes the sizes; 1: the general kernel
   p.scale = (float)scale;
   p.dtype = dtype_code(q, "q");
   p.status = status_ptr(status);
@@ -997,7 +997,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("tile_nq"), py::arg("partials"), py::arg("num_tiles"), py::arg("q_tile"), py::arg("num_splits"),
         py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("v_dim"), py::arg("window"), py::arg("chunk"),
         py::arg("scale"), py::arg("softcap"), py::arg("slopes") = py::none(), py::arg("gate") = py::none(),
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), py::arg("kernel") = 0);
   m.def("head_prep", &head_prep, py::arg("x"), py::arg("slots"), py::arg("q_out"), py::arg("k_cache"),
         py::arg("v_cache"), py::arg("v_keep"), py::arg("v_other"), py::arg("blend_weight"), py::arg("gate_out"),
         py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("v_dim"), py::arg("unit_norm"),

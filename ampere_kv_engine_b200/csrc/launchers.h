@@ -201,6 +201,14 @@ struct ScoredAttentionParams {
   const float* gate;           // [N, NH] or null: a head's output is multiplied by its gate
 };
 int launch_scored_attention(const ScoredAttentionParams& p, cudaStream_t stream);
+// The tcgen05 prompt kernel's scored form (attention_tcgen05.cu): bfloat16 prompt tiles with keys and values of 128
+// dims, whatever modifiers; `base.kernel` == 1 keeps the general kernel.
+// The mma.sync decode kernel's scored form (attention_tc.cu): single-token tiles with keys and values of the same 64
+// or 128 dims, 1, 2, 4 or 8 key splits.
+bool attention_tc_scored_supported(const ScoredAttentionParams& p);
+int launch_attention_tc_scored(const ScoredAttentionParams& p, cudaStream_t stream);
+bool attention_tcgen05_scored_supported(const ScoredAttentionParams& p);
+int launch_attention_tcgen05_scored(const ScoredAttentionParams& p, cudaStream_t stream);
 
 // What stands between one product that holds [q heads | k heads | v heads | a gate column per q head] of every token
 // and the attention over them (mixer_prep.cu): q and k heads scaled to unit RMS, v blended with another layer's

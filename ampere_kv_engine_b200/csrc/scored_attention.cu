@@ -309,6 +309,9 @@ int launch_scored_attention(const ScoredAttentionParams& sp, cudaStream_t stream
   if (p.head_dim < 1 || sp.v_dim < 1 || sp.v_dim > 512 || p.num_heads % p.num_kv_heads || p.num_splits < 1 ||
       sp.k_row_stride < p.head_dim || sp.v_row_stride < sp.v_dim || sp.chunk < 0 || sp.softcap < 0.f)
     return (int)cudaErrorInvalidValue;
+  if (p.kernel != 1 && p.q_tile > 1 && attention_tcgen05_scored_supported(sp))
+    return launch_attention_tcgen05_scored(sp, stream);
+  if (p.kernel != 1 && p.q_tile == 1 && attention_tc_scored_supported(sp)) return launch_attention_tc_scored(sp, stream);
   return p.dtype == kBFloat16 ? launch_scored_typed<__nv_bfloat16>(sp, stream)
                               : launch_scored_typed<float>(sp, stream);
 }

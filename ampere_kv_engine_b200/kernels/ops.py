@@ -252,16 +252,27 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, 
     return out
 
 
+def scored_takes_tensor_cores(dtype: torch.dtype, head_dim: int, v_dim: int, group_size: int, page_size: int,
+                              prompt: bool) -> bool:
+    """Whether the tensor-core kernels' scored forms take these sizes: bfloat16 keys and values of the same width in
+    storage of their own; prompt tiles at 128 dims on the tcgen05 kernel, single tokens at 64 or 128 dims on the
+    TMA + mma.sync decode kernel (1, 2, 4 or 8 key splits).  Everything else runs on the general kernel."""
+    if dtype != torch.bfloat16 or head_dim != v_dim or not 1 <= group_size <= 16 or page_size & (page_size - 1):
+        return False
+    return (head_dim == 128 and page_size >= 16) if prompt else (head_dim in (64, 128) and page_size >= 8)
+
+
 def scored_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq, *, num_tiles,
                      q_tile, num_splits, num_heads, num_kv_heads, v_dim, scale, window=0, chunk=0, softcap=0.0,
-                     slopes=None, gate=None, partials=None, status=None, out=None):
+                     slopes=None, gate=None, partials=None, status=None, out=None, kernel: str = "auto"):
     """Causal attention of the batch's new tokens over paged keys and values of different widths, with the score
     reshaped before the softmax: ``softcap * tanh(score / softcap)`` (``softcap`` > 0), less ``slopes[h]`` times the
     distance to the key (``slopes`` float32 [heads]); a query sees the last ``window`` keys (``window`` > 0) of its own
     block of ``chunk`` positions (``chunk`` > 0); ``gate`` (float32 [tokens, heads]) scales each head's output.
     ``k_cache`` / ``v_cache``: [pages, kv heads, page size, width]; they may be one tensor whose rows are read whole
     as keys and in their first ``v_dim`` elements as values.  Returns [tokens, heads * v_dim]; only the rows of the
-    given tiles are written."""
+    given tiles are written.  ``kernel``: ``"auto"`` takes the tensor-core kernels where they fit
+    (:func:`scored_takes_tensor_cores`), ``"general"`` keeps the general kernel."""
     if out is None:
         out = torch.empty((q.shape[0], num_heads * v_dim), dtype=q.dtype, device=q.device)
     if num_splits > 1 and partials is None:
@@ -269,7 +280,8 @@ def scored_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq,
                                device=q.device)
     ext().scored_attention(q, k_cache, v_cache, out, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq, partials,
                            num_tiles, q_tile, num_splits, num_heads, num_kv_heads, int(v_dim), int(window or 0),
-                           int(chunk or 0), float(scale), float(softcap or 0.0), slopes, gate, status)
+                           int(chunk or 0), float(scale), float(softcap or 0.0), slopes, gate, status,
+                           {"auto": 0, "general": 1}[kernel])
     _launched(2 if num_splits > 1 else 1)
     return out
 

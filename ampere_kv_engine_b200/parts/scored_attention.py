@@ -69,6 +69,11 @@ class ScoredAttention(Mixer):
             self.slopes = torch.exp2(-self.slope_span * h / self.num_heads).to(torch.float32).to(self.device)
         self.w_in = self.w_o = self.blend_weight = None
 
+    def preferred_q_tile(self):
+        if self.head_dim == self.v_dim == 128:
+            return ops.attention_q_tile(self.head_dim, self.num_heads // self.num_kv_heads)
+        return None
+
     def cache_spec(self) -> CacheSpec:
         kind = "chunk" if self.chunk else ("window" if self.window else "full")
         return CacheSpec(kind=kind, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
@@ -143,7 +148,10 @@ def run_attention(ctx, group, q, k_cache, v_cache, out, *, num_heads, num_kv_hea
         for limit in (window, chunk):
             if limit:
                 longest, mean = min(longest, limit), min(mean, limit)
-        splits = ops.choose_splits(hi - lo, num_kv_heads, q_tile * group_size, longest, False, mean_context=mean)
+        tensor_core = k_cache is not v_cache and ops.scored_takes_tensor_cores(
+            q.dtype, q.shape[1] // num_heads, v_dim, group_size, k_cache.shape[2], prompt=q_tile > 1)
+        splits = 1 if q_tile > 1 and tensor_core else ops.choose_splits(
+            hi - lo, num_kv_heads, q_tile * group_size, longest, tensor_core, mean_context=mean)
         ops.scored_attention(
             q, k_cache, v_cache, group.block_table, ctx.cu_q, ctx.ctx_lens, ctx.tile_seq[lo:hi], ctx.tile_q0[lo:hi],
             ctx.tile_nq[lo:hi], num_tiles=hi - lo, q_tile=q_tile, num_splits=splits, num_heads=num_heads,

@@ -448,6 +448,193 @@ def long_context_shape(args) -> int:
     return 0
 
 
+# Sukalorn at sizes that resemble a real model's layers, and the Qwen3 layers they are set beside: the same width,
+# heads, head size and feed-forward width.  Four layers each (Sukalorn: attention, latent, attention, latent).
+SUKALORN_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, q_rank=768, kv_rank=512, rot_dim=64, block=1024),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, q_rank=1536, kv_rank=512, rot_dim=64, block=1024),
+}
+SUKALORN_VOCAB = 32000
+SUKALORN_LAYERS = 4
+
+
+def sukalorn_config(z: dict, layers: int) -> dict:
+    attention = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                 "scale": z["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": z["block"]}, "v_mix": True}
+    latent = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot_dim"], "vdim": z["dim"], "q_rank": z["q_rank"],
+              "kv_rank": z["kv_rank"], "scale": (z["dim"] + z["rot_dim"]) ** -0.5,
+              "rot": {"base": 10000.0, "dims": z["rot_dim"]}}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    return {"architecture": "Sukalorn", "vocab": SUKALORN_VOCAB, "width": z["width"], "norm": {"eps": 1e-6},
+            "layers": [{"type": "attention" if i % 2 == 0 else "latent_attention",
+                        "mixer": dict(attention if i % 2 == 0 else latent), "mlp": dict(mlp)} for i in range(layers)]}
+
+
+def qwen3_like(z: dict, layers: int) -> dict:
+    return dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=z["width"], num_attention_heads=z["heads"],
+                num_key_value_heads=z["kv_heads"], head_dim=z["dim"], intermediate_size=z["ff"],
+                vocab_size=SUKALORN_VOCAB)
+
+
+def sukalorn_shape(args) -> int:
+    """Prefill (one 2,048-token prompt) and decode (batch 8 from 1,024-token prompts) of the Sukalorn design at two
+    layer sizes, each beside Qwen3 layers of the same width, heads, head size and feed-forward width, through the
+    engine's own step function; then the attention kernels alone at the same shapes, each with the fraction of the
+    measured peak it reaches (prompt: FLOPs over the burst bf16 product peak; decode: cache bytes over the copy
+    bandwidth).  ``value`` is Sukalorn's decode tokens per second at the larger size."""
+    import torch
+    from ampere_kv_engine_b200.config.engine_config import EngineConfig
+    from ampere_kv_engine_b200.engine.batch import SeqStep
+    from ampere_kv_engine_b200.engine.engine import Engine
+    from ampere_kv_engine_b200.kernels import ops
+    from ampere_kv_engine_b200.sampling.sampler import SamplingParams
+    peaks = load_peaks()
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    layers = args.layers or SUKALORN_LAYERS
+    batch = args.batch
+    gen = torch.Generator().manual_seed(1234)
+    flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device=device)      # larger than the 126 MB L2
+
+    def timed(fn, steps, flush_l2=False):
+        total = 0.0
+        for _ in range(steps):
+            if flush_l2:
+                flush.zero_()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            fn()
+            stop.record()
+            torch.cuda.synchronize()
+            total += start.elapsed_time(stop)
+        return total / steps
+
+    def measure(config: dict) -> dict:
+        engine = Engine.from_random(config, seed=0, device=device, config=EngineConfig(
+            dtype="bfloat16", page_size=args.page_size, max_tokens=(batch + 1) * (PROMPT_LEN + GEN_LEN + 64) + PREFILL_TOKENS,
+            max_seqs=batch + 2, max_batch_tokens=PREFILL_TOKENS, max_context=CONTEXT))
+        runner, vocab = engine.runner, engine.vocab_size
+        synthetic = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+        prompt = synthetic(PREFILL_TOKENS)
+
+        def prefill_once():
+            seq = runner.open("prefill")
+            logits = runner.step([SeqStep(seq, prompt, [PREFILL_TOKENS - 1])])
+            engine.sampler.sample(logits, [SamplingParams()], [0])
+            runner.close(seq)
+
+        for _ in range(3):
+            prefill_once()
+        prefill_ms = timed(prefill_once, 5)
+        seqs = [runner.open(f"d{i}") for i in range(batch)]
+        for i in range(0, batch, 2):
+            runner.step([SeqStep(s, synthetic(PROMPT_LEN), []) for s in seqs[i:i + 2]])
+        greedy, zeros = [SamplingParams()] * batch, [0] * batch
+
+        def one():
+            logits = runner.step([SeqStep(s, [t], [0]) for s, t in zip(seqs, synthetic(batch))])
+            engine.sampler.sample(logits, greedy, zeros)
+
+        for _ in range(args.warmup):
+            one()
+        ops.launch_count = 0
+        decode_ms = timed(one, args.steps)
+        launches = ops.launch_count // args.steps
+        runner.raise_on_status()
+        weights = sum(t.numel() * t.element_size() for part in engine.model._parts() for t in vars(part).values()
+                      if isinstance(t, torch.Tensor) and t.dim() >= 2)
+        del engine, runner, seqs
+        torch.cuda.empty_cache()
+        return {"prefill_ms": round(prefill_ms, 3), "prefill_tok_s": round(PREFILL_TOKENS / prefill_ms * 1000, 1),
+                "decode_ms": round(decode_ms, 4), "decode_tok_s": round(batch / decode_ms * 1000, 1),
+                "launches_per_decode_step": launches, "matrix_bytes": weights,
+                "decode_hbm_frac_weights_only": round(weights / (decode_ms / 1000) / 1e9 / peaks["hbm_gbs"], 4)}
+
+    def kernels_alone(z: dict) -> dict:
+        """The attention kernels by themselves at this size: a 2,048-token prompt as one sequence, and single tokens
+        of `batch` sequences that each hold 1,024 keys."""
+        out = {}
+        page, heads, kvh, dim = args.page_size, z["heads"], z["kv_heads"], z["dim"]
+        row = z["kv_rank"] + z["rot_dim"]
+        bf = dict(dtype=torch.bfloat16, device=device)
+        g = torch.Generator(device=device).manual_seed(1)
+
+        def layout(seq_q, q_tile):
+            cu, tiles = [0], []
+            for s, (_, n) in enumerate(seq_q):
+                tiles += [(s, cu[-1] + t0, min(q_tile, n - t0)) for t0 in range(0, n, q_tile)]
+                cu.append(cu[-1] + n)
+            pages_per = [(c + page - 1) // page for c, _ in seq_q]
+            table = torch.full((len(seq_q), max(pages_per)), -1, dtype=torch.int32)
+            at = 0
+            for s, n in enumerate(pages_per):
+                table[s, :n] = torch.arange(at, at + n, dtype=torch.int32)
+                at += n
+            dev = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+            return dict(block_table=table.to(device), cu_q=dev(cu), ctx_lens=dev([c for c, _ in seq_q]),
+                        tile_seq=dev([t[0] for t in tiles]), tile_q0=dev([t[1] for t in tiles]),
+                        tile_nq=dev([t[2] for t in tiles]), num_tiles=len(tiles), q_tile=q_tile), at, cu[-1]
+
+        for name, seq_q, q_tile in (("prompt", [(PREFILL_TOKENS, PREFILL_TOKENS)], ops.ATTENTION_Q_TILE),
+                                    ("decode", [(PROMPT_LEN, 1)] * batch, 1)):
+            lay, pages, tokens = layout(seq_q, q_tile)
+            keys = sum(c for c, _ in seq_q)
+            pairs = sum(n * (2 * c - n + 1) // 2 for c, n in seq_q)           # (query, visible key) pairs, causal
+            rand = lambda *shape: torch.randn(shape, generator=g, **bf)
+            k_pages, v_pages, rows = rand(pages, kvh, page, dim), rand(pages, kvh, page, dim), rand(pages, 1, page, row)
+            q, q_row = rand(tokens, heads * dim), rand(tokens, heads * row)
+            slopes = torch.exp2(-8.0 * torch.arange(1, heads + 1, device=device) / heads).float()
+            gate = torch.rand((tokens, heads), device=device, generator=g)
+            group = heads // kvh
+            cases = {
+                "qwen3_attention": (lambda s: ops.paged_attention(
+                    q, k_pages, v_pages, num_splits=s, num_heads=heads, num_kv_heads=kvh, window=0, scale=dim ** -0.5,
+                    **lay), 4.0 * heads * dim * pairs, 2.0 * 2 * kvh * dim * keys,
+                    ops.choose_splits(lay["num_tiles"], kvh, q_tile * group, PROMPT_LEN, True) if q_tile == 1 else 1),
+                "sukalorn_attention": (lambda s: ops.scored_attention(
+                    q, k_pages, v_pages, num_splits=s, num_heads=heads, num_kv_heads=kvh, v_dim=dim, scale=dim ** -0.5,
+                    softcap=30.0, slopes=slopes, gate=gate, chunk=0, **lay), 4.0 * heads * dim * pairs,
+                    2.0 * 2 * kvh * dim * keys, ops.choose_splits(lay["num_tiles"], kvh, q_tile * group, PROMPT_LEN, False)),
+                "sukalorn_latent_attention": (lambda s: ops.scored_attention(
+                    q_row, rows, rows, num_splits=s, num_heads=heads, num_kv_heads=1, v_dim=z["kv_rank"],
+                    scale=0.07, **lay), 2.0 * heads * (row + z["kv_rank"]) * pairs, 2.0 * row * keys,
+                    ops.choose_splits(lay["num_tiles"], 1, q_tile * heads, PROMPT_LEN, False)),
+            }
+            for case, (fn, flops, cache_bytes, splits) in cases.items():
+                for _ in range(3):
+                    fn(splits)
+                ms = timed(lambda: fn(splits), 5, flush_l2=True)
+                entry = {"ms": round(ms, 4), "splits": splits}
+                if name == "prompt":
+                    entry["tflops"] = round(flops / (ms / 1000) / 1e12, 2)
+                    entry["frac_of_bf16_peak"] = round(flops / (ms / 1000) / 1e12 / peaks["bf16_tflops"], 4)
+                else:
+                    entry["cache_gbs"] = round(cache_bytes / (ms / 1000) / 1e9, 1)
+                    entry["frac_of_hbm"] = round(cache_bytes / (ms / 1000) / 1e9 / peaks["hbm_gbs"], 4)
+                out[f"{name}_{case}"] = entry
+        return out
+
+    sizes = {}
+    with ClockSampler() as clocks:
+        for name, z in SUKALORN_SIZES.items():
+            sizes[name] = {"sukalorn": measure(sukalorn_config(z, layers)), "qwen3": measure(qwen3_like(z, layers)),
+                           "kernels": kernels_alone(z)}
+    head = sizes["4k"]["sukalorn"]
+    line = {"metric": "decode tok/s at batch 8 of four Sukalorn layers (width 4,096, B200); prefill, a smaller size, "
+                      "Qwen3 layers of equal size and the attention kernels alone alongside",
+            "value": head["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": head["decode_ms"], "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic (seeded uniform token ids, seeded random weights)",
+            "config": {"model": "Sukalorn", "layers": layers, "sizes": SUKALORN_SIZES, "vocab": SUKALORN_VOCAB,
+                       "global_batch": batch, "prompt_len": PROMPT_LEN, "prefill_tokens": PREFILL_TOKENS,
+                       "page_size": args.page_size, "l2": "whole steps: inputs larger than L2; kernels alone: L2 "
+                       "flushed (a 256 MB write) before every timed launch", "peaks": peaks["source"]},
+            "gpu_launches": head["launches_per_decode_step"] * args.steps, "sizes": sizes, "clocks": clocks.summary()}
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -455,15 +642,25 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page (a power of two, 16 or more)")
-    parser.add_argument("--shape", choices=sorted(SHAPES), default="8b",
+    parser.add_argument("--shape", choices=sorted(SHAPES) + ["sukalorn"], default="8b",
                         help="8b: the headline benchmark; 14b: a mixed scheduler load of 64 requests; 32b: long-context "
-                             "decode at batch 16 (each prints its own one line)")
+                             "decode at batch 16; sukalorn: prefill and decode of the Sukalorn design at two layer "
+                             "sizes beside Qwen3 layers of equal size (each prints its own one line)")
     parser.add_argument("--layers", type=int, default=None,
                         help="run fewer layers of the same sizes (reported in config beside the full count)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
     args = parser.parse_args()
 
+    if args.shape == "sukalorn":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference arm runs the 8b shape only"}))
+            return 0
+        if args.gpus != 1:
+            print(json.dumps({"error": "this engine runs on one GPU; --gpus must be 1", "n_gpus": args.gpus}))
+            return 2
+        args.warmup = max(3, args.warmup)
+        return sukalorn_shape(args)
     if args.layers is None:
         args.layers = SHAPES[args.shape]["num_hidden_layers"]
     if args.impl == "reference":

@@ -135,7 +135,7 @@ class FakeExt:
 
     def scored_attention(self, q, k_cache, v_cache, out, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq,
                          partials, num_tiles, q_tile, num_splits, num_heads, num_kv_heads, v_dim, window, chunk, scale,
-                         softcap, slopes=None, gate=None, status=None):
+                         softcap, slopes=None, gate=None, status=None, kernel=0):
         page_size = k_cache.shape[2]
         d = q.shape[1] // num_heads
         group = num_heads // num_kv_heads

@@ -9,7 +9,8 @@ The configurations differ from one another in every size and in the order of the
 * ``S2``: attention first; as many key/value heads as query heads; one key/value head in another layer; blocks of 7
   and of 64 positions in different layers (two cache groups); a layer without blocks or cap; a rotation over fewer
   dims than the rotated part has.
-* ``S3``: head and latent widths at which 16-byte key loads and the small-batch product kernel run.
+* ``S3``: head and latent widths at which 16-byte key loads, the small-batch product kernel and the tensor-core
+  attention kernels' scored forms run (keys and values of 128 dims: prompt and decode; of 64 dims: decode).
 
 Random matrices of N(0, 0.02) would leave every softmax nearly flat; the folders' query/key matrices of the latent
 mixers are scaled up so that attention weights differ by orders of magnitude.
@@ -69,9 +70,10 @@ S2 = {
 S3 = {
     "architecture": "Sukalorn", "vocab": 320, "width": 256, "norm": {"eps": 1e-6},
     "layers": [
-        _layer("attention", _attention(4, 2, 128, 64, 0.09, size=96, softcap=10.0, v_mix=True), 512),
+        _layer("attention", _attention(4, 2, 128, 128, 0.09, size=96, softcap=10.0, v_mix=True), 512),
         _layer("latent_attention", _latent(4, 64, 32, 64, 96, 128, 0.1, 10000.0), 512),
-        _layer("attention", _attention(4, 2, 128, 64, 0.09, size=96, softcap=10.0, v_mix=True), 512),
+        _layer("attention", _attention(4, 2, 128, 128, 0.09, size=96, softcap=10.0, v_mix=True), 512),
+        _layer("attention", _attention(8, 1, 64, 64, 0.12, size=40, softcap=3.0, v_mix=False), None),
     ],
 }
 CONFIGS = {"S1": (S1, 16), "S2": (S2, 32), "S3": (S3, 16)}

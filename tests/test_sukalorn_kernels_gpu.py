@@ -139,8 +139,7 @@ def _dense_attention(q, k, v, *, first_pos, scale, softcap, slopes, chunk, windo
     return out if gate is None else out * gate[:, :, None]
 
 
-def _run_scored(ops, dtype, q, keys, values, tables, seq_q, *, heads, kv_heads, v_dim, page_size, q_tile, splits, same_rows=False,
-                **score):
+def _run_scored(ops, dtype, q, keys, values, tables, seq_q, *, heads, kv_heads, v_dim, page_size, q_tile, splits, **score):
     """One call over sequences given as (context length, new tokens): q rows are the new tokens of all sequences."""
     cu = [0]
     for _, n in seq_q:
@@ -249,3 +248,60 @@ def test_a_latent_row_read_as_key_and_value(dtype):
                                 softcap=0.0, slopes=None, chunk=0, window=0, gate=None)
         torch.testing.assert_close(out[at:at + n].double().cpu().view(n, heads, v_dim), want, **TOL[dtype])
         at += n
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,chunk,softcap,biased,gated", [
+    (8, 2, 128, 96, 10.0, True, True), (4, 4, 128, 0, 0.0, True, False), (6, 2, 128, 50, 3.0, False, True),
+    (8, 1, 64, 40, 3.0, True, True), (5, 1, 128, 200, 30.0, True, True)])
+def test_tensor_core_forms_match_the_plain_formula_and_the_general_kernel(heads, kv_heads, dim, chunk, softcap, biased, gated):
+    """bfloat16 keys and values of the same 64 or 128 dims: prompt tiles on the tcgen05 kernel's scored form (128
+    dims), single tokens on the decode kernel's (1, 2, 4 and 8 key splits), against the float64 formula and, more
+    tightly, against the general kernel on the same inputs.  Positions are chosen at block edges; pages of blocks the
+    sequence has left are not held (-1 in the table) and hold NaN."""
+    ops = _ops()
+    dtype, page_size, scale = torch.bfloat16, 16, 0.1
+    g = torch.Generator(device="cuda").manual_seed(77)
+    slopes = plain.distance_slopes(heads) if biased else None
+    c3 = chunk * 3 or 300
+    group = heads // kv_heads
+    q_tile = ops.attention_q_tile(dim, group)
+    cases = [([(c3, 1), (c3 + 1, 1), (c3 - 1, 1), (700, 1), (1, 1)], 1, (1, 2, 4, 8))]
+    if dim == 128:
+        cases.append(([(300, 300), (c3 + 37, 90), (3, 2), (c3, 1)], q_tile, (1,)))
+    for seq_q, tile, split_counts in cases:
+        num_pages = sum((c + page_size - 1) // page_size for c, _ in seq_q) + 2
+        k_pages, v_pages = _pages(1, num_pages, kv_heads, page_size, dim, dtype), _pages(2, num_pages, kv_heads, page_size, dim, dtype)
+        order = torch.randperm(num_pages, generator=torch.Generator().manual_seed(4)).tolist()
+        width = max((c + page_size - 1) // page_size for c, _ in seq_q)
+        table = torch.full((len(seq_q), width), -1, dtype=torch.int32)
+        for s, (c, n) in enumerate(seq_q):
+            first_needed = ((c - n) // chunk * chunk) if chunk else 0
+            for j in range((c + page_size - 1) // page_size):
+                page = order.pop()
+                if (j + 1) * page_size <= first_needed:          # a page the sequence has given back
+                    k_pages[page], v_pages[page] = float("nan"), float("nan")
+                else:
+                    table[s, j] = page
+        total = sum(n for _, n in seq_q)
+        q = (3 * torch.randn((total, heads * dim), generator=g, device="cuda")).to(dtype)
+        gate = torch.rand((total, heads), generator=g, device="cuda") if gated else None
+        score = dict(scale=scale, chunk=chunk, softcap=softcap, slopes=None if slopes is None else slopes.float().cuda(), gate=gate)
+        common = dict(heads=heads, kv_heads=kv_heads, v_dim=dim, page_size=page_size, q_tile=tile)
+        general = _run_scored(ops, dtype, q, k_pages, v_pages, table.cuda(), seq_q, splits=1, kernel="general", **common, **score)
+        for splits in split_counts:
+            out = _run_scored(ops, dtype, q, k_pages, v_pages, table.cuda(), seq_q, splits=splits, **common, **score)
+            torch.testing.assert_close(out.float(), general.float(), atol=6e-3, rtol=2e-2)
+            row = 0
+            for s, (c, n) in enumerate(seq_q):
+                first_needed = ((c - n) // chunk * chunk) if chunk else 0
+                keys = torch.arange(c)
+                pages = table[s].long()[keys // page_size].clamp(min=0)
+                k = k_pages.cpu()[pages, :, keys % page_size].double()
+                v = v_pages.cpu()[pages, :, keys % page_size].double()
+                k[:first_needed // page_size * page_size] = 0
+                v[:first_needed // page_size * page_size] = 0
+                want = _dense_attention(q[row:row + n].double().cpu().view(n, heads, dim), k, v, first_pos=c - n, scale=scale,
+                                        softcap=softcap, slopes=slopes, chunk=chunk, window=0,
+                                        gate=None if gate is None else gate[row:row + n].double().cpu())
+                torch.testing.assert_close(out[row:row + n].double().cpu().view(n, heads, dim), want, **TOL[dtype])
+                row += n
