@@ -253,6 +253,17 @@ __global__ void scored_merge_kernel(const float* __restrict__ partials, T* __res
   }
 }
 
+template <typename T>
+static int launch_scored_merge(const ScoredAttentionParams& sp, cudaStream_t stream) {
+  const PagedAttentionParams& p = sp.base;
+  const int64_t merge_blocks = (int64_t)p.num_tiles * p.q_tile * p.num_heads;
+  if (merge_blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  const int threads = sp.v_dim <= 32 ? 32 : (sp.v_dim <= 64 ? 64 : 128);
+  scored_merge_kernel<T><<<(unsigned)merge_blocks, threads, 0, stream>>>(
+      p.partials, (T*)p.out, p.tile_q0, p.tile_nq, sp.gate, p.q_tile, p.num_heads, p.num_splits, sp.v_dim);
+  return (int)cudaGetLastError();
+}
+
 template <typename T, int DC, int R>
 static int launch_rows(const ScoredAttentionParams& sp, cudaStream_t stream) {
   const PagedAttentionParams& p = sp.base;
@@ -275,15 +286,7 @@ static int launch_rows(const ScoredAttentionParams& sp, cudaStream_t stream) {
   kernel<<<(unsigned)blocks, kScoredWarps * 32, smem, stream>>>(sp, row_groups, total, vec);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return (int)err;
-  if (p.num_splits > 1) {
-    const int64_t merge_blocks = (int64_t)p.num_tiles * p.q_tile * p.num_heads;
-    if (merge_blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
-    const int threads = sp.v_dim <= 32 ? 32 : (sp.v_dim <= 64 ? 64 : 128);
-    scored_merge_kernel<T><<<(unsigned)merge_blocks, threads, 0, stream>>>(
-        p.partials, (T*)p.out, p.tile_q0, p.tile_nq, sp.gate, p.q_tile, p.num_heads, p.num_splits, sp.v_dim);
-    return (int)cudaGetLastError();
-  }
-  return 0;
+  return p.num_splits > 1 ? launch_scored_merge<T>(sp, stream) : 0;
 }
 
 template <typename T>
@@ -312,6 +315,11 @@ int launch_scored_attention(const ScoredAttentionParams& sp, cudaStream_t stream
   if (p.kernel != 1 && p.q_tile > 1 && attention_tcgen05_scored_supported(sp))
     return launch_attention_tcgen05_scored(sp, stream);
   if (p.kernel != 1 && p.q_tile == 1 && attention_tc_scored_supported(sp)) return launch_attention_tc_scored(sp, stream);
+  if (p.kernel != 1 && scored_attention_mma_supported(sp)) {
+    const int err = launch_scored_attention_mma(sp, stream);
+    if (err != 0) return err;
+    return p.num_splits > 1 ? launch_scored_merge<__nv_bfloat16>(sp, stream) : 0;
+  }
   return p.dtype == kBFloat16 ? launch_scored_typed<__nv_bfloat16>(sp, stream)
                               : launch_scored_typed<float>(sp, stream);
 }

@@ -262,6 +262,24 @@ def scored_takes_tensor_cores(dtype: torch.dtype, head_dim: int, v_dim: int, gro
     return (head_dim == 128 and page_size >= 16) if prompt else (head_dim in (64, 128) and page_size >= 8)
 
 
+def shared_rows_take_tensor_cores(dtype: torch.dtype, row: int, v_dim: int) -> bool:
+    """Whether the mma.sync kernel for rows that are key and value at once takes these sizes (bfloat16, a key width
+    that is a multiple of 16, a value width of 64, 128, 256 or 512)."""
+    return dtype == torch.bfloat16 and row % 16 == 0 and 16 <= row <= 1024 and v_dim in (64, 128, 256, 512) \
+        and v_dim <= row
+
+
+def choose_splits_shared_rows(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_context: int,
+                              sms: int | None = None) -> int:
+    """Key splits for the shared-row kernel: a CTA per (tile, kv head, 16 rows, split), two to an SM; a split walks
+    at least 64 keys."""
+    sms = sms or sm_count()
+    items = max(1, num_tiles * num_kv_heads * ((rows_per_tile + 15) // 16))
+    if items >= 2 * sms or max_context <= 128:
+        return 1
+    return int(max(1, min(2 * sms // items, (max_context + 63) // 64, 32)))
+
+
 def scored_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq, *, num_tiles,
                      q_tile, num_splits, num_heads, num_kv_heads, v_dim, scale, window=0, chunk=0, softcap=0.0,
                      slopes=None, gate=None, partials=None, status=None, out=None, kernel: str = "auto"):

@@ -150,8 +150,13 @@ def run_attention(ctx, group, q, k_cache, v_cache, out, *, num_heads, num_kv_hea
                 longest, mean = min(longest, limit), min(mean, limit)
         tensor_core = k_cache is not v_cache and ops.scored_takes_tensor_cores(
             q.dtype, q.shape[1] // num_heads, v_dim, group_size, k_cache.shape[2], prompt=q_tile > 1)
-        splits = 1 if q_tile > 1 and tensor_core else ops.choose_splits(
-            hi - lo, num_kv_heads, q_tile * group_size, longest, tensor_core, mean_context=mean)
+        if k_cache is v_cache and ops.shared_rows_take_tensor_cores(q.dtype, q.shape[1] // num_heads, v_dim):
+            splits = ops.choose_splits_shared_rows(hi - lo, num_kv_heads, q_tile * group_size, longest)
+        elif q_tile > 1 and tensor_core:
+            splits = 1
+        else:
+            splits = ops.choose_splits(hi - lo, num_kv_heads, q_tile * group_size, longest, tensor_core,
+                                       mean_context=mean)
         ops.scored_attention(
             q, k_cache, v_cache, group.block_table, ctx.cu_q, ctx.ctx_lens, ctx.tile_seq[lo:hi], ctx.tile_q0[lo:hi],
             ctx.tile_nq[lo:hi], num_tiles=hi - lo, q_tile=q_tile, num_splits=splits, num_heads=num_heads,

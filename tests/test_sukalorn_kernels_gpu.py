@@ -305,3 +305,37 @@ def test_tensor_core_forms_match_the_plain_formula_and_the_general_kernel(heads,
                                         gate=None if gate is None else gate[row:row + n].double().cpu())
                 torch.testing.assert_close(out[row:row + n].double().cpu().view(n, heads, dim), want, **TOL[dtype])
                 row += n
+
+
+@pytest.mark.parametrize("heads,row,v_dim,window", [(5, 160, 128, 0), (16, 576, 512, 0), (3, 96, 64, 70), (20, 272, 256, 0)])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_shared_rows_on_tensor_cores(heads, row, v_dim, window, splits):
+    """bfloat16 rows read as key and value on the mma.sync kernel: prompt tiles (a whole prompt, a portion behind a long
+    context, a short one) and single tokens, one split and several, against the float64 formula and the general
+    kernel."""
+    ops = _ops()
+    dtype, page_size, scale = torch.bfloat16, 16, 0.05
+    g = torch.Generator(device="cuda").manual_seed(13)
+    for seq_q, q_tile in (([(130, 130), (400, 45), (3, 2), (65, 1)], 32), ([(257, 1), (32, 1), (1, 1), (700, 1)], 1)):
+        num_pages = sum((c + page_size - 1) // page_size for c, _ in seq_q) + 2
+        rows = _pages(5, num_pages, 1, page_size, row, dtype)
+        order = torch.randperm(num_pages, generator=torch.Generator().manual_seed(6)).tolist()
+        width = max((c + page_size - 1) // page_size for c, _ in seq_q)
+        table = torch.full((len(seq_q), width), -1, dtype=torch.int32)
+        for s, (c, _) in enumerate(seq_q):
+            for j in range((c + page_size - 1) // page_size):
+                table[s, j] = order.pop()
+        total = sum(n for _, n in seq_q)
+        q = torch.randn((total, heads * row), generator=g, device="cuda").to(dtype)
+        common = dict(heads=heads, kv_heads=1, v_dim=v_dim, page_size=page_size, q_tile=q_tile, scale=scale, window=window)
+        general = _run_scored(ops, dtype, q, rows, rows, table.cuda(), seq_q, splits=1, kernel="general", **common)
+        out = _run_scored(ops, dtype, q, rows, rows, table.cuda(), seq_q, splits=splits, **common)
+        torch.testing.assert_close(out.float(), general.float(), atol=6e-3, rtol=2e-2)
+        at = 0
+        for s, (c, n) in enumerate(seq_q):
+            pages = table[s].long()[torch.arange(c) // page_size]
+            k = rows.cpu()[pages, :, torch.arange(c) % page_size].double()
+            want = _dense_attention(q[at:at + n].double().cpu().view(n, heads, row), k, k[..., :v_dim], first_pos=c - n,
+                                    scale=scale, softcap=0.0, slopes=None, chunk=0, window=window, gate=None)
+            torch.testing.assert_close(out[at:at + n].double().cpu().view(n, heads, v_dim), want, **TOL[dtype])
+            at += n
