@@ -208,7 +208,7 @@ int launch_scored_attention(const ScoredAttentionParams& p, cudaStream_t stream)
 bool attention_tc_scored_supported(const ScoredAttentionParams& p);
 int launch_attention_tc_scored(const ScoredAttentionParams& p, cudaStream_t stream);
 // The mma.sync kernel for rows that are key and value at once (scored_attention_mma.cu): bfloat16, k_cache == v_cache,
-// key width a multiple of 16, value width 64, 128, 256 or 512; any tiles and splits (without the merge).
+// key width a multiple of 16 up to 576, value width 64, 128, 256 or 512; any tiles and splits (without the merge).
 bool scored_attention_mma_supported(const ScoredAttentionParams& p);
 int launch_scored_attention_mma(const ScoredAttentionParams& p, cudaStream_t stream);
 bool attention_tcgen05_scored_supported(const ScoredAttentionParams& p);

@@ -264,8 +264,8 @@ def scored_takes_tensor_cores(dtype: torch.dtype, head_dim: int, v_dim: int, gro
 
 def shared_rows_take_tensor_cores(dtype: torch.dtype, row: int, v_dim: int) -> bool:
     """Whether the mma.sync kernel for rows that are key and value at once takes these sizes (bfloat16, a key width
-    that is a multiple of 16, a value width of 64, 128, 256 or 512)."""
-    return dtype == torch.bfloat16 and row % 16 == 0 and 16 <= row <= 1024 and v_dim in (64, 128, 256, 512) \
+    that is a multiple of 16 up to 576, a value width of 64, 128, 256 or 512)."""
+    return dtype == torch.bfloat16 and row % 16 == 0 and 16 <= row <= 576 and v_dim in (64, 128, 256, 512) \
         and v_dim <= row
 
 
