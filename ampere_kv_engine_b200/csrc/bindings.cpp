@@ -258,10 +258,13 @@ void check_cluster_splits(int64_t splits, int64_t k) {
 // silu(gate) * up, [tokens, features / 2] bfloat16.
 void small_m_gemm(const OptTensor& x, const Tensor& w, Tensor& out, int64_t splits, const OptTensor& status,
                   bool gated, const OptTensor& nx_hidden, const OptTensor& nx_ssq, const OptTensor& nx_weight,
-                  double nx_eps) {
+                  double nx_eps, int64_t activation) {
   const TokenOperand t = token_operand(x, nx_hidden, nx_ssq, nx_weight, nx_eps, w);
   check_cuda(out, "out");
   AKV_CHECK(out.device() == w.device(), "out and w must be on the same device");
+  AKV_CHECK(activation >= -1 && activation <= 2 &&
+                (activation < 0 || (!gated && out.dim() == 2 && out.scalar_type() == at::kBFloat16)),
+            "an activation (0 relu squared, 1 tanh GELU, 2 SiLU) goes with the plain product and a bfloat16 out");
   void* out_ptr = nullptr;
   float* parts_ptr = nullptr;
   int out_code = 0;
@@ -291,6 +294,7 @@ void small_m_gemm(const OptTensor& x, const Tensor& w, Tensor& out, int64_t spli
   f.epilogue = gated ? akv::kEpilogueGated : akv::kEpiloguePlain;
   f.normed_x = t.is_normed;
   f.normed = t.normed;
+  f.activation = (int)activation;
   c10::cuda::CUDAGuard guard(w.device());
   check_launch(akv::launch_small_m_gemm(t.x, w.data_ptr(), out_ptr, out_code, parts_ptr, t.tokens, w.size(0), t.k,
                                         (int)splits, &f, status_ptr(status), stream_of(*t.anchor)),
@@ -970,7 +974,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("silu_mul", &silu_mul, py::arg("gate_up"), py::arg("out"), py::arg("block") = 0);
   m.def("small_m_gemm", &small_m_gemm, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("splits") = 1,
         py::arg("status") = py::none(), py::arg("gated") = false, py::arg("nx_hidden") = py::none(),
-        py::arg("nx_ssq") = py::none(), py::arg("nx_weight") = py::none(), py::arg("nx_eps") = 0.0);
+        py::arg("nx_ssq") = py::none(), py::arg("nx_weight") = py::none(), py::arg("nx_eps") = 0.0,
+        py::arg("activation") = -1);
   m.def("small_m_gemm_residual", &small_m_gemm_residual, py::arg("x"), py::arg("w"), py::arg("hidden"),
         py::arg("ssq"), py::arg("splits") = 1, py::arg("status") = py::none());
   m.def("small_m_gemm_qkv", &small_m_gemm_qkv, py::arg("x"), py::arg("w"), py::arg("q_out"), py::arg("positions"),

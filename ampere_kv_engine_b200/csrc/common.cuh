@@ -74,6 +74,16 @@ __device__ __forceinline__ float silu_mul_value(float g, float u) {
   else return g / (1.f + expf(-g)) * u;
 }
 
+// The element-wise activations of launchers.h's Activation: 0 = relu(z)^2, 1 = the tanh form of GELU, 2 = SiLU.
+__device__ __forceinline__ float activation_value(float z, int kind) {
+  if (kind == 0) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+  }
+  if (kind == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.f + expf(-z));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -110,6 +110,7 @@ struct GemmParams {
   GemmQkv qkv;            // kEpilogueQkv only
   GemmResidual residual;  // kEpilogueResidual only
   GemmNormedX normed;     // kNormedX only
+  int activation;         // kEpiloguePlain, bfloat16 out: applied to the rounded product; -1: none
 };
 
 template <int BN, int kStages>
@@ -576,7 +577,13 @@ small_m_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
               if (lane == 0) p.residual.ssq[(int64_t)tile * p.tokens + tok] = ss;
             } else {
               OutT* dst = out + (int64_t)tok * p.features + feature;
-              const float x[4] = {v.x, v.y, v.z, v.w};
+              float x[4] = {v.x, v.y, v.z, v.w};
+              if constexpr (sizeof(OutT) == 2) {
+                if (p.activation >= 0) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) x[i] = activation_value(bf16_round(x[i]), p.activation);
+                }
+              }
               if (whole && feature < p.features) {
                 if constexpr (sizeof(OutT) == 4) {
                   *reinterpret_cast<float4*>(dst) = v;
@@ -794,7 +801,10 @@ int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, 
   if (!matrix_map(w, features, k, kTileM, &w_map)) return (int)cudaErrorInvalidValue;
   if (f.normed_x) x_map = w_map;      // unused
   else if (!matrix_map(x, tokens, k, bn, &x_map)) return (int)cudaErrorInvalidValue;
-  GemmParams p{parts, out, (int)tokens, (int)features, (int)k, kb_total, splits, status, f.qkv, f.residual, f.normed};
+  if (f.activation >= 0 && (f.epilogue != kEpiloguePlain || out == nullptr || out_dtype != kBFloat16 || f.activation > 2))
+    return (int)cudaErrorInvalidValue;
+  GemmParams p{parts, out, (int)tokens, (int)features, (int)k, kb_total, splits, status, f.qkv, f.residual, f.normed,
+               f.activation};
   const bool bf16_out = out != nullptr && out_dtype == kBFloat16;
   if (f.normed_x) return launch_tokens<true>(bn, w_map, x_map, p, f.epilogue, bf16_out, stream);
   return launch_tokens<false>(bn, w_map, x_map, p, f.epilogue, bf16_out, stream);

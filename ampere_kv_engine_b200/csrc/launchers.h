@@ -93,6 +93,9 @@ struct GemmFusion {
   GemmResidual residual = {};
   bool normed_x = false;     // x is null and normed says how to make it
   GemmNormedX normed = {};
+  // kEpiloguePlain with a bfloat16 out only: an Activation applied to the product (rounded to bfloat16 first, as the
+  // stored product would be) before it is stored; -1: none
+  int activation = -1;
 };
 int launch_small_m_gemm(const void* x, const void* w, void* out, int out_dtype, float* parts, int64_t tokens,
                         int64_t features, int64_t k, int splits, const GemmFusion* fusion, int* status,

@@ -218,16 +218,6 @@ int launch_rotate_pairs(const void* in, void* out, const int32_t* positions, con
 }
 
 template <typename T>
-__device__ __forceinline__ float activate(float z, int kind) {
-  if (kind == kActReluSquared) {
-    const float r = fmaxf(z, 0.f);
-    return r * r;
-  }
-  if (kind == kActGeluTanh) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-  return z / (1.f + expf(-z));
-}
-
-template <typename T>
 __global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t total, int kind) {
   pdl_launch_dependents();
   pdl_wait();
@@ -237,7 +227,7 @@ __global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out,
     float v[8];
     load8<T>(in + idx, v);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = activate<T>(v[i], kind);
+    for (int i = 0; i < 8; ++i) v[i] = activation_value(v[i], kind);
     if constexpr (sizeof(T) == 2) {
       uint4 raw;
       __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
@@ -250,7 +240,7 @@ __global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out,
     }
     return;
   }
-  for (int64_t i = idx; i < min(idx + 8, total); ++i) out[i] = from_float<T>(activate<T>(to_float<T>(in[i]), kind));
+  for (int64_t i = idx; i < min(idx + 8, total); ++i) out[i] = from_float<T>(activation_value(to_float<T>(in[i]), kind));
 }
 
 int launch_activation(const void* in, void* out, int64_t total, int kind, int dtype, cudaStream_t stream) {

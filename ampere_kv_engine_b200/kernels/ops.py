@@ -341,6 +341,16 @@ def rotate_pairs(x, out, positions, inv_freq, *, heads, cols, rotary_dims, in_of
 ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
 
 
+def linear_activation(x, weight: torch.Tensor, kind: str, status: torch.Tensor | None = None) -> torch.Tensor:
+    """``activation(x @ weight.T)``, the activation applied to the product as it is stored (rounded to the compute
+    dtype).  Few bfloat16 tokens: one launch of the small-batch product kernel, whose output tile goes through the
+    activation; otherwise the library product and the activation kernel.  ``x`` may be a ``LazyNorm``."""
+    x, normed, small = _operand(x, weight)
+    if small:
+        return small_m_gemm(x, weight, status=status, normed=normed, activation=kind)
+    return activation(torch.nn.functional.linear(x, weight), kind)
+
+
 def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
     """``relu(x) ** 2`` (``"relu2"``), the tanh form of GELU (``"gelu_tanh"``) or SiLU, element by element."""
     out = torch.empty_like(x)
@@ -443,7 +453,7 @@ def _cluster_splits(weight: torch.Tensor) -> int:
 
 def small_m_gemm(x: torch.Tensor | None, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
                  splits: int | None = None, parts: bool = False, status: torch.Tensor | None = None,
-                 gated: bool = False, normed: dict | None = None) -> torch.Tensor:
+                 gated: bool = False, normed: dict | None = None, activation: str | None = None) -> torch.Tensor:
     """``x @ weight.T`` for 1..64 bfloat16 tokens on the tcgen05 tensor cores, K cut into ``splits`` ranges.
 
     Default: [tokens, features] in ``out_dtype`` (float32 or bfloat16); the splits (1, 2, 4 or 8 CTAs of a
@@ -451,7 +461,8 @@ def small_m_gemm(x: torch.Tensor | None, weight: torch.Tensor, out_dtype: torch.
     partial sums themselves, [splits, tokens, features], for a consumer kernel that adds them up.
     ``gated=True``: ``weight`` holds gate and up rows in alternating runs of 64 and the result is
     ``silu(gate) * up``, [tokens, features / 2] bfloat16.  ``normed`` (with ``x`` None): the kernel makes its token
-    operand from a residual stream and its sums of squares (``LazyNorm``).
+    operand from a residual stream and its sums of squares (``LazyNorm``).  ``activation`` (a name of
+    ``ACTIVATIONS``; bfloat16 result only): applied to the product, rounded to bfloat16 first, before it is stored.
     """
     normed = normed or {}
     tokens = x.shape[0] if x is not None else normed["nx_hidden"].shape[0]
@@ -466,7 +477,10 @@ def small_m_gemm(x: torch.Tensor | None, weight: torch.Tensor, out_dtype: torch.
             splits -= 1
         out = torch.empty((tokens, weight.shape[0] // 2 if gated else weight.shape[0]),
                           dtype=torch.bfloat16 if gated else out_dtype, device=weight.device)
-    ext().small_m_gemm(x, weight, out, splits, status, gated, **normed)
+    if activation is not None:
+        ext().small_m_gemm(x, weight, out, splits, status, gated, activation=ACTIVATIONS[activation], **normed)
+    else:
+        ext().small_m_gemm(x, weight, out, splits, status, gated, **normed)
     _launched()
     return out
 

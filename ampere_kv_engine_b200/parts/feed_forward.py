@@ -103,7 +103,7 @@ class DenseMLP(FeedForward):
 
     def forward(self, x, ctx, residual=None):
         status = getattr(ctx, "status", None)
-        act = ops.activation(ops.linear(x, self.up, status=status), self.activation)
+        act = ops.linear_activation(x, self.up, self.activation, status=status)
         if residual is not None:
             summed = ops.linear_into_residual(act, self.down, residual, status=status)
             if summed is not None:

@@ -339,3 +339,19 @@ def test_shared_rows_on_tensor_cores(heads, row, v_dim, window, splits):
                                     scale=scale, softcap=0.0, slopes=None, chunk=0, window=window, gate=None)
             torch.testing.assert_close(out[at:at + n].double().cpu().view(n, heads, v_dim), want, **TOL[dtype])
             at += n
+
+
+@pytest.mark.parametrize("tokens,features,k", [(1, 384, 192), (8, 512, 256), (33, 200, 72), (64, 1024, 512)])
+@pytest.mark.parametrize("kind", ["relu2", "gelu_tanh", "silu"])
+def test_product_with_the_activation_on_its_output_tile(tokens, features, k, kind):
+    """The small-batch product kernel's activation against the product followed by the activation kernel: both round
+    the product to bfloat16 first, so they agree to the last bit but for the sums' order."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(tokens)
+    x = torch.randn((tokens, k), generator=g, device="cuda").bfloat16()
+    w = (torch.randn((features, k), generator=g, device="cuda") / k ** 0.5).bfloat16()
+    fused = ops.linear_activation(x, w, kind)
+    plain_product = (x.double() @ w.double().T).float().bfloat16()
+    want = ops.activation(plain_product, kind)
+    torch.testing.assert_close(fused.float(), want.float(), atol=2e-2, rtol=2e-2)
+    assert float((fused.float() - want.float()).abs().mean()) < 2e-3
