@@ -103,16 +103,15 @@ int launch_head_prep(const HeadPrepParams& p, cudaStream_t stream) {
   return (int)launch_chain(head_prep_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, dim3(1, 1, 1), p);
 }
 
-// One warp per (token, segment): 0 = query latent, 1 = key/value latent, 2 = rotated key part.
+// One block per (token, segment): 0 = query latent, 1 = key/value latent, 2 = rotated key part.  (A warp per segment
+// walked a latent of several hundred elements in a dozen dependent rounds: 14 us for 8 tokens.)
 template <typename T>
-__global__ void latent_prep_kernel(LatentPrepParams p) {
+__global__ void __launch_bounds__(128) latent_prep_kernel(LatentPrepParams p) {
+  __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (item >= p.num_tokens * 3) return;
-  const int64_t token = item / 3;
-  const int segment = (int)(item - token * 3);
+  const int64_t token = blockIdx.x / 3;
+  const int segment = (int)(blockIdx.x - token * 3);
   const int64_t width = (int64_t)p.q_rank + p.kv_rank + p.rot_dim;
   const T* x = (const T*)p.x + token * width;
   const int slot = p.slots != nullptr ? p.slots[token] : -1;
@@ -123,14 +122,14 @@ __global__ void latent_prep_kernel(LatentPrepParams p) {
     const T* src = x + (segment == 0 ? 0 : p.q_rank);
     const float* w = segment == 0 ? p.q_weight : p.kv_weight;
     T* dst = segment == 0 ? (T*)p.q_latent + token * (int64_t)p.q_rank : row;
-    if (n == 0 || dst == nullptr) return;
+    if (n == 0 || dst == nullptr) return;                  // the same for every thread of the block
     float ss = 0.f;
-    for (int d = lane; d < n; d += 32) {
+    for (int d = threadIdx.x; d < n; d += blockDim.x) {
       const float v = to_float<T>(src[d]);
       ss += v * v;
     }
-    const float inv = rsqrtf(warp_sum(ss) / (float)n + p.eps);
-    for (int d = lane; d < n; d += 32) dst[d] = from_float<T>(to_float<T>(src[d]) * inv * w[d]);
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)n + p.eps);
+    for (int d = threadIdx.x; d < n; d += blockDim.x) dst[d] = from_float<T>(to_float<T>(src[d]) * inv * w[d]);
     return;
   }
   if (row == nullptr) return;
@@ -138,7 +137,7 @@ __global__ void latent_prep_kernel(LatentPrepParams p) {
   T* dst = row + p.kv_rank;
   const float position = (float)p.positions[token];
   const int pairs = p.rot_dim / 2, turning = p.rotary_dims / 2;
-  for (int i = lane; i < pairs; i += 32) {
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
     float u = to_float<T>(src[2 * i]), v = to_float<T>(src[2 * i + 1]);
     if (i < turning) {
       float sn, cs;
@@ -150,20 +149,18 @@ __global__ void latent_prep_kernel(LatentPrepParams p) {
     dst[2 * i] = from_float<T>(u);
     dst[2 * i + 1] = from_float<T>(v);
   }
-  if ((p.rot_dim & 1) && lane == 0) dst[p.rot_dim - 1] = src[p.rot_dim - 1];
+  if ((p.rot_dim & 1) && threadIdx.x == 0) dst[p.rot_dim - 1] = src[p.rot_dim - 1];
 }
 
 int launch_latent_prep(const LatentPrepParams& p, cudaStream_t stream) {
   if (p.num_tokens == 0) return 0;
   if (p.rotary_dims > p.rot_dim || (p.rotary_dims & 1)) return (int)cudaErrorInvalidValue;
-  const int warps = 4;
-  const int64_t blocks = (p.num_tokens * 3 + warps - 1) / warps;
+  const int64_t blocks = p.num_tokens * 3;
   if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
   if (p.dtype == kBFloat16)
-    return (int)launch_chain(latent_prep_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
+    return (int)launch_chain(latent_prep_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(128), 0, stream,
                              dim3(1, 1, 1), p);
-  return (int)launch_chain(latent_prep_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
-                           dim3(1, 1, 1), p);
+  return (int)launch_chain(latent_prep_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, stream, dim3(1, 1, 1), p);
 }
 
 // One thread per (token, head, pair of the column range).

@@ -217,12 +217,16 @@ scored_attention_kernel(ScoredAttentionParams sp, int row_groups, int64_t total_
 }
 
 // out[row] = gate[row] * sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s, splits taken in order; one block per
-// (tile, row of the tile, q-head), so only the rows of the call's tiles are written.
+// (tile, row of the tile, q-head), so only the rows of the call's tiles are written.  The splits' weights are worked
+// out once per block (thread s takes split s) and left in shared memory; after that a thread only adds up its dims.
+constexpr int kMergeSplits = 64;       // most key splits of a call
 template <typename T>
 __global__ void scored_merge_kernel(const float* __restrict__ partials, T* __restrict__ out,
                                     const int32_t* __restrict__ tile_q0, const int32_t* __restrict__ tile_nq,
                                     const float* __restrict__ gate, int q_tile, int num_heads, int num_splits,
                                     int v_dim) {
+  __shared__ float weight[kMergeSplits];
+  __shared__ float scale_out;
   pdl_launch_dependents();
   pdl_wait();
   const int64_t per_tile = (int64_t)q_tile * num_heads;
@@ -232,24 +236,44 @@ __global__ void scored_merge_kernel(const float* __restrict__ partials, T* __res
   if (r >= tile_nq[tile]) return;
   const int64_t row = ((int64_t)tile_q0[tile] + r) * num_heads + head;
   const float* base = partials + row * num_splits * (int64_t)(v_dim + 2);
-  float m = -CUDART_INF_F;
-  for (int s = 0; s < num_splits; ++s) {
-    const float* part = base + (int64_t)s * (v_dim + 2);
-    if (part[v_dim + 1] > 0.f) m = fmaxf(m, part[v_dim]);
-  }
-  const float g = gate != nullptr ? gate[row] : 1.f;
-  for (int d = threadIdx.x; d < v_dim; d += blockDim.x) {
-    float num = 0.f, den = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-      const float* part = base + (int64_t)s * (v_dim + 2);
-      const float ls = part[v_dim + 1];
-      if (ls > 0.f) {
-        const float w = expf(part[v_dim] - m);
-        num += w * part[d];
-        den += w * ls;
+  if (threadIdx.x < 32) {
+    // one warp: the maximum over the splits, each split's weight, the weighted sum of the row sums in split order
+    float ms[(kMergeSplits + 31) / 32], ls[(kMergeSplits + 31) / 32];
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int c = 0; c < (kMergeSplits + 31) / 32; ++c) {
+      const int s = c * 32 + threadIdx.x;
+      ms[c] = -CUDART_INF_F;
+      ls[c] = 0.f;
+      if (s < num_splits) {
+        const float* part = base + (int64_t)s * (v_dim + 2);
+        ls[c] = part[v_dim + 1];
+        if (ls[c] > 0.f) ms[c] = part[v_dim];
       }
+      m = fmaxf(m, ms[c]);
     }
-    out[row * v_dim + d] = from_float<T>(den > 0.f ? g * num / den : 0.f);
+    m = warp_max(m);
+#pragma unroll
+    for (int c = 0; c < (kMergeSplits + 31) / 32; ++c) {
+      const int s = c * 32 + threadIdx.x;
+      if (s < num_splits) weight[s] = ls[c] > 0.f ? expf(ms[c] - m) : 0.f;
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) {
+      float den = 0.f;
+      for (int s = 0; s < num_splits; ++s) den += weight[s] * base[(int64_t)s * (v_dim + 2) + v_dim + 1];
+      scale_out = den > 0.f ? (gate != nullptr ? gate[row] : 1.f) / den : 0.f;
+    }
+  }
+  __syncthreads();
+  const float g = scale_out;
+  for (int d = threadIdx.x; d < v_dim; d += blockDim.x) {
+    float num = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float w = weight[s];
+      if (w > 0.f) num += w * base[(int64_t)s * (v_dim + 2) + d];
+    }
+    out[row * v_dim + d] = from_float<T>(g * num);
   }
 }
 
@@ -259,9 +283,9 @@ static int launch_scored_merge(const ScoredAttentionParams& sp, cudaStream_t str
   const int64_t merge_blocks = (int64_t)p.num_tiles * p.q_tile * p.num_heads;
   if (merge_blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
   const int threads = sp.v_dim <= 32 ? 32 : (sp.v_dim <= 64 ? 64 : 128);
-  scored_merge_kernel<T><<<(unsigned)merge_blocks, threads, 0, stream>>>(
-      p.partials, (T*)p.out, p.tile_q0, p.tile_nq, sp.gate, p.q_tile, p.num_heads, p.num_splits, sp.v_dim);
-  return (int)cudaGetLastError();
+  return (int)launch_chain(scored_merge_kernel<T>, dim3((unsigned)merge_blocks), dim3(threads), 0, stream, dim3(1, 1, 1),
+                           (const float*)p.partials, (T*)p.out, p.tile_q0, p.tile_nq, sp.gate, p.q_tile, p.num_heads,
+                           p.num_splits, sp.v_dim);
 }
 
 template <typename T, int DC, int R>
@@ -283,8 +307,8 @@ static int launch_rows(const ScoredAttentionParams& sp, cudaStream_t stream) {
   const int per16 = 16 / (int)sizeof(T);
   const int vec = (p.head_dim % 8 == 0 && sp.k_row_stride % per16 == 0 &&
                    reinterpret_cast<uintptr_t>(p.k_cache) % 16 == 0) ? 1 : 0;
-  kernel<<<(unsigned)blocks, kScoredWarps * 32, smem, stream>>>(sp, row_groups, total, vec);
-  cudaError_t err = cudaGetLastError();
+  cudaError_t err = launch_chain(kernel, dim3((unsigned)blocks), dim3(kScoredWarps * 32), smem, stream, dim3(1, 1, 1), sp,
+                                 row_groups, total, vec);
   if (err != cudaSuccess) return (int)err;
   return p.num_splits > 1 ? launch_scored_merge<T>(sp, stream) : 0;
 }
@@ -310,6 +334,7 @@ int launch_scored_attention(const ScoredAttentionParams& sp, cudaStream_t stream
   const PagedAttentionParams& p = sp.base;
   if (p.num_tiles == 0 || p.num_tokens == 0) return 0;
   if (p.head_dim < 1 || sp.v_dim < 1 || sp.v_dim > 512 || p.num_heads % p.num_kv_heads || p.num_splits < 1 ||
+      p.num_splits > kMergeSplits ||
       sp.k_row_stride < p.head_dim || sp.v_row_stride < sp.v_dim || sp.chunk < 0 || sp.softcap < 0.f)
     return (int)cudaErrorInvalidValue;
   if (p.kernel != 1 && p.q_tile > 1 && attention_tcgen05_scored_supported(sp))

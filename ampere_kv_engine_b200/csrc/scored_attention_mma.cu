@@ -366,8 +366,7 @@ static int launch_mma(const ScoredAttentionParams& sp, cudaStream_t stream) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
   }
-  kernel<<<(unsigned)blocks, 128, smem, stream>>>(sp, row_groups, ldk);
-  return (int)cudaGetLastError();
+  return (int)launch_chain(kernel, dim3((unsigned)blocks), dim3(128), smem, stream, dim3(1, 1, 1), sp, row_groups, ldk);
 }
 
 int launch_scored_attention_mma(const ScoredAttentionParams& sp, cudaStream_t stream) {

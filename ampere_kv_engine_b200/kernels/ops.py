@@ -272,12 +272,12 @@ def shared_rows_take_tensor_cores(dtype: torch.dtype, row: int, v_dim: int) -> b
 def choose_splits_shared_rows(num_tiles: int, num_kv_heads: int, rows_per_tile: int, max_context: int,
                               sms: int | None = None) -> int:
     """Key splits for the shared-row kernel: a CTA per (tile, kv head, 16 rows, split), two to an SM; a split walks
-    at least 64 keys."""
+    at least 128 keys (every split writes a partial row of the value width per head, and a merge reads them)."""
     sms = sms or sm_count()
     items = max(1, num_tiles * num_kv_heads * ((rows_per_tile + 15) // 16))
-    if items >= 2 * sms or max_context <= 128:
+    if items >= 2 * sms or max_context <= 256:
         return 1
-    return int(max(1, min(2 * sms // items, (max_context + 63) // 64, 32)))
+    return int(max(1, min(2 * sms // items, (max_context + 127) // 128, 32)))
 
 
 def scored_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, tile_nq, *, num_tiles,
