@@ -90,6 +90,9 @@ class ModelSpec:
     head: PartSpec
     max_position: int
     eos_token_ids: tuple[int, ...] = ()
+    #: tensors a checkpoint may carry although nothing uses them (full name -> shape): accepted when present, never
+    #: asked for (the second norm of a layer that has no feed-forward, for instance)
+    unused_tensors: tuple[tuple[str, tuple[int, ...]], ...] = ()
 
     def validate(self) -> None:
         if not self.schedule:

@@ -57,6 +57,8 @@ class DecoderModel:
                 if name in out and out[name] != ps:
                     raise ValueError(f"tensor {name} is declared twice with different shapes")
                 out[name] = ps
+        for name, shape in self.spec.unused_tensors:
+            out.setdefault(name, ParamSpec(tuple(shape), kind="vector", optional=True))
         return out
 
     def load_tensors(self, tensors: dict[str, torch.Tensor]) -> None:

@@ -24,7 +24,7 @@ def _norm(config: SukalornConfig, prefix: str, tensor: str) -> PartSpec:
 
 
 def build_spec(config: SukalornConfig) -> ModelSpec:
-    layers = []
+    layers, unused = [], []
     blending_seen = False
     for i, layer in enumerate(config.layers):
         prefix, m = f"l{i}", layer.mixer
@@ -53,6 +53,8 @@ def build_spec(config: SukalornConfig) -> ModelSpec:
             ff = PartSpec("dense_mlp", {"intermediate_size": layer.mlp["ff"], "activation": "relu2", "up": "up",
                                         "down": "down"}, f"{prefix}.mlp")
             ff_norm = _norm(config, prefix, "norm2")
+        else:
+            unused.append((f"{prefix}.norm2", (config.width,)))     # a layer without a feed-forward may still carry it
         layers.append(LayerSpec(block="prenorm", mixer=mixer, feed_forward=ff, mixer_norm=_norm(config, prefix, "norm1"),
                                 feed_forward_norm=ff_norm))
     return ModelSpec(
@@ -66,6 +68,7 @@ def build_spec(config: SukalornConfig) -> ModelSpec:
         head=PartSpec("linear_head", {"vocab_size": config.vocab, "tied": False, "tensor": "head"}, ""),
         max_position=config.max_position_embeddings,
         eos_token_ids=config.eos_token_id,
+        unused_tensors=tuple(unused),
     )
 
 

@@ -88,9 +88,8 @@ class ScoredAttention(Mixer):
             n["k"]: ParamSpec((self.num_kv_heads * self.head_dim, h)),
             n["v"]: ParamSpec((self.num_kv_heads * self.v_dim, h)),
         }
-        if self.value_blend is not None:
-            # a source layer carries the scalar too and does not use it
-            specs[n["blend"]] = ParamSpec((), kind="vector", init="unit_interval")
+        # a source layer carries the scalar too and does not use it; a layer that does not blend may carry it
+        specs[n["blend"]] = ParamSpec((), kind="vector", init="unit_interval", optional=self.value_blend is None)
         if self.gated:
             specs[n["gate"]] = ParamSpec((self.num_heads, h))
         specs[n["out"]] = ParamSpec((h, self.num_heads * self.v_dim))

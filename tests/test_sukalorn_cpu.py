@@ -42,10 +42,14 @@ def test_spec_gives_blending_layers_their_roles_and_layers_their_parts():
     assert [l.feed_forward is None for l in spec.layers] == [False, False, True, False, True]
     assert spec.layers[1].mixer.params["chunk"] == 20 and spec.layers[1].mixer.params["softcap"] == 2.0
     from ampere_kv_engine_b200.models.decoder import DecoderModel
-    names = set(DecoderModel(spec, dtype=torch.float32, device="cpu").param_specs())
+    specs = DecoderModel(spec, dtype=torch.float32, device="cpu").param_specs()
+    wanted = {name for name, ps in specs.items() if not ps.optional}
     assert {"embed", "embed.norm", "final.norm", "head", "l0.mix.dq.norm", "l1.mix.vmix", "l1.mix.g", "l3.mlp.down",
-            "l0.norm2", "l2.norm1"} <= names
-    assert "l2.norm2" not in names and "l2.mlp.up" not in names
+            "l0.norm2", "l2.norm1"} <= wanted
+    # a layer without a feed-forward wants no second norm, a layer that does not blend no blend scalar; a checkpoint
+    # may still carry them
+    assert "l2.mlp.up" not in specs and not ({"l2.norm2", "l3.mix.vmix"} & wanted)
+    assert specs["l2.norm2"].optional and specs["l3.mix.vmix"].optional
 
 
 def test_block_cache_gives_pages_back_once_a_sequence_has_left_the_block():
@@ -120,3 +124,25 @@ def test_a_reader_without_a_source_is_refused(fake_ext):
     with pytest.raises(ValueError, match="no layer before"):
         runner.step([SeqStep(runner.open("a"), [1, 2, 3], [2])])
     assert runner.manager.free_pages() == [8]
+
+
+def test_a_checkpoint_may_carry_tensors_of_parts_a_layer_does_not_have(fake_ext, tmp_path):
+    """The second norm of a layer without a feed-forward and the blend scalar of a layer that does not blend are
+    accepted when a checkpoint has them, and change nothing."""
+    import os
+    import shutil
+    from safetensors.torch import load_file, save_file
+    from ampere_kv_engine_b200.engine.engine import Engine
+    raw, page = su.CONFIGS["S1"]
+    folder = su.model_folder("S1")
+    copy_dir = str(tmp_path / "with_extras")
+    shutil.copytree(folder, copy_dir)
+    tensors = load_file(os.path.join(copy_dir, "model.safetensors"))
+    assert "l2.norm2" not in tensors and "l3.mix.vmix" not in tensors
+    tensors["l2.norm2"] = torch.full((raw["width"],), 0.5)
+    tensors["l3.mix.vmix"] = torch.tensor(0.9)
+    save_file(tensors, os.path.join(copy_dir, "model.safetensors"), metadata={"format": "pt"})
+    prompts = [[5, 7, 11, 13, 17, 19, 23]]
+    a = Engine.from_pretrained(folder, dtype="float32", device="cpu", page_size=page, num_pages=8, max_seqs=2)
+    b = Engine.from_pretrained(copy_dir, dtype="float32", device="cpu", page_size=page, num_pages=8, max_seqs=2)
+    assert a.generate(prompts, max_new_tokens=4, ignore_eos=True) == b.generate(prompts, max_new_tokens=4, ignore_eos=True)
