@@ -1,6 +1,6 @@
 """Benchmark of the engine on one B200: decode tokens per second at the Qwen3-8B shape.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference] [--shape 8b|14b|32b|sukalorn]
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch through the engine's own step
 function (every kernel of the model and the token choice); ``value`` is batch / step time, timed with CUDA
@@ -9,6 +9,8 @@ step copies that step's token ids and index data from pinned host memory to the 
 chosen tokens back.  ``prefill`` is one 2,048-token prompt in one step; ``points`` holds decode at batch 1
 and 64; ``roofline`` compares the bytes a decode step must read (every weight once, the live requests'
 cache) with the copy bandwidth.  Weights are random (seeded), token ids synthetic (seeded uniform).
+``--shape sukalorn`` prints a line of its own: prefill and decode of four Sukalorn layers at two sizes beside Qwen3
+layers of equal size, and the attention kernels alone.
 Between timed steps nothing is flushed: every step streams the whole model (16 GB at full depth) through
 a 126 MB L2, so the inputs are larger than L2.
 """
