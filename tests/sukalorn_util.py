@@ -71,7 +71,7 @@ S3 = {
     "architecture": "Sukalorn", "vocab": 320, "width": 256, "norm": {"eps": 1e-6},
     "layers": [
         _layer("attention", _attention(4, 2, 128, 128, 0.09, size=96, softcap=10.0, v_mix=True), 512),
-        _layer("latent_attention", _latent(20, 64, 32, 64, 96, 128, 0.1, 10000.0), 512),
+        _layer("latent_attention", _latent(20, 48, 16, 40, 96, 256, 0.1, 10000.0), 512),
         _layer("attention", _attention(4, 2, 128, 128, 0.09, size=96, softcap=10.0, v_mix=True), 512),
         _layer("attention", _attention(8, 1, 64, 64, 0.12, size=40, softcap=3.0, v_mix=False), None),
     ],
