@@ -9,6 +9,7 @@ field of a dataclass parsed from config.json; no size stands anywhere else in th
 
 from __future__ import annotations
 
+import copy
 import json
 import os
 from dataclasses import dataclass, fields
@@ -326,6 +327,148 @@ class SukalornConfig:
                           for l in self.layers]}
         if self.max_position_embeddings != 1 << 20:
             out["max_position_embeddings"] = self.max_position_embeddings
+        if self.eos_token_id:
+            out["eos_token_id"] = list(self.eos_token_id)
+        return out
+
+
+@dataclass(frozen=True)
+class ZifuzenLayer:
+    """One entry of ``layers``: the mixer's ``type``, its sizes and constants as config.json gives them, and the
+    feed-forward (None: the layer has none)."""
+
+    type: str
+    mixer: dict
+    mlp: dict | None
+
+    #: both delta types are the gated delta rule
+    MIXERS = ("attention", "delta", "delta_2")
+
+
+@dataclass(frozen=True)
+class ZifuzenConfig:
+    """config.json of the ``Zifuzen`` decoder: ``vocab``, ``width``, ``max_positions`` (rows of the learned
+    position table), ``embedding.scale``, ``norm.eps``, ``logit_softcap`` and a list of layers.  A layer names its
+    mixer (``attention``: grouped queries with a weighted RMS norm on queries and keys, no rotation, optionally the
+    keys and values of an earlier layer, ``kv_from``; ``delta`` / ``delta_2``: the gated delta rule behind short
+    convolutions) and its feed-forward (``dense`` with biases and tanh GELU, ``moe`` with a sigmoid router over groups
+    of experts and an optional shared expert, or none).  Every size and constant is read from here."""
+
+    vocab: int
+    width: int
+    max_positions: int
+    embedding_scale: float
+    norm_eps: float
+    logit_softcap: float | None
+    layers: tuple[ZifuzenLayer, ...]
+    eos_token_id: tuple[int, ...] = ()
+    architectures: tuple[str, ...] = ("Zifuzen",)
+
+    ARCHITECTURE = "Zifuzen"
+
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @property
+    def max_position_embeddings(self) -> int:
+        return self.max_positions
+
+    @staticmethod
+    def _check_expert(d: dict, where: str) -> None:
+        _sized(d, "ff", where)
+        if _number(d, "limit", where) <= 0:
+            raise ConfigError(f"config.json: {where}'limit' must be positive")
+
+    @classmethod
+    def _check_mlp(cls, mlp: dict, where: str) -> None:
+        kind = mlp.get("kind", "dense")
+        if kind == "dense":
+            _sized(mlp, "ff", where)
+            return
+        if kind != "moe":
+            raise ConfigError(f"config.json: {where}'kind' must be 'dense' or 'moe', got {kind!r}")
+        cls._check_expert(_section(mlp, "expert", where), where + "expert: ")
+        router = _section(mlp, "router", where)
+        where_r = where + "router: "
+        experts, top = _sized(router, "experts", where_r), _sized(router, "top", where_r)
+        _number(router, "scale", where_r)
+        count = keep = 1
+        if router.get("groups") is not None:
+            groups = _section(router, "groups", where_r)
+            count, keep = _sized(groups, "count", where_r + "groups: "), _sized(groups, "keep", where_r + "groups: ")
+        if experts % count or keep > count:
+            raise ConfigError(f"config.json: {where_r}groups: 'count' ({count}) must divide 'experts' ({experts}) and "
+                              f"'keep' ({keep}) must not exceed it")
+        if top > keep * (experts // count):
+            raise ConfigError(f"config.json: {where_r}'top' ({top}) is more than the {keep} kept groups of "
+                              f"{experts // count} experts hold")
+        if mlp.get("shared") is not None:
+            cls._check_expert(_section(mlp, "shared", where), where + "shared: ")
+
+    @classmethod
+    def from_dict(cls, d: dict[str, Any]) -> "ZifuzenConfig":
+        layers_raw = d.get("layers")
+        if not isinstance(layers_raw, (list, tuple)) or not layers_raw:
+            raise ConfigError("config.json: key 'layers' must be a non-empty list")
+        layers = []
+        for i, entry in enumerate(layers_raw):
+            where = f"layers[{i}]: "
+            if not isinstance(entry, dict) or entry.get("type") not in ZifuzenLayer.MIXERS:
+                raise ConfigError(f"config.json: {where}'type' must be one of {list(ZifuzenLayer.MIXERS)}, "
+                                  f"got {entry.get('type') if isinstance(entry, dict) else entry!r}")
+            mixer = _section(entry, "mixer", where)
+            where_m = where + "mixer: "
+            for key in ("heads", "kv_heads", "dim", "vdim"):
+                _sized(mixer, key, where_m)
+            if mixer["heads"] % mixer["kv_heads"]:
+                raise ConfigError(f"config.json: {where_m}'heads' ({mixer['heads']}) must be a multiple of "
+                                  f"'kv_heads' ({mixer['kv_heads']})")
+            if entry["type"] == "attention":
+                _number(mixer, "scale", where_m)
+                source = mixer.get("kv_from")
+                if source is not None:
+                    ok = isinstance(source, int) and not isinstance(source, bool) and 0 <= source < i
+                    other = layers[source] if ok else None
+                    if other is None or other.type != "attention" or other.mixer.get("kv_from") is not None:
+                        raise ConfigError(f"config.json: {where_m}'kv_from' must name an earlier attention layer that "
+                                          f"has keys and values of its own, got {source!r}")
+                    if any(other.mixer[k] != mixer[k] for k in ("kv_heads", "dim", "vdim")):
+                        raise ConfigError(f"config.json: {where_m}'kv_from': layer {source} keeps keys and values of "
+                                          f"another shape")
+            else:
+                _sized(mixer, "conv", where_m)
+            mlp = entry.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict):
+                    raise ConfigError(f"config.json: {where}'mlp' must be an object or null")
+                cls._check_mlp(mlp, where + "mlp: ")
+            layers.append(ZifuzenLayer(entry["type"], dict(mixer), None if mlp is None else copy.deepcopy(mlp)))
+        eos = d.get("eos_token_id")
+        eos = () if eos is None else ((eos,) if isinstance(eos, int) else tuple(eos))
+        cap = d.get("logit_softcap")
+        cfg = cls(
+            vocab=_sized(d, "vocab", ""),
+            width=_sized(d, "width", ""),
+            max_positions=_sized(d, "max_positions", ""),
+            embedding_scale=_number(_section(d, "embedding", ""), "scale", "embedding: "),
+            norm_eps=_number(_section(d, "norm", ""), "eps", "norm: "),
+            logit_softcap=None if cap is None else _number(d, "logit_softcap", ""),
+            layers=tuple(layers),
+            eos_token_id=eos,
+        )
+        if cfg.norm_eps <= 0:
+            raise ConfigError("config.json: norm: 'eps' must be positive")
+        if cfg.logit_softcap is not None and cfg.logit_softcap <= 0:
+            raise ConfigError("config.json: 'logit_softcap' must be positive (or null for none)")
+        return cfg
+
+    def to_dict(self) -> dict[str, Any]:
+        out = {"architecture": self.ARCHITECTURE, "vocab": self.vocab, "width": self.width,
+               "max_positions": self.max_positions, "embedding": {"scale": self.embedding_scale},
+               "norm": {"eps": self.norm_eps}, "logit_softcap": self.logit_softcap,
+               "layers": [{"type": l.type, "mixer": dict(l.mixer), "mlp": None if l.mlp is None else copy.deepcopy(l.mlp)}
+                          for l in self.layers]}
         if self.eos_token_id:
             out["eos_token_id"] = list(self.eos_token_id)
         return out

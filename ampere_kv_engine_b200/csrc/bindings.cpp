@@ -102,7 +102,7 @@ void wait_selftest(int64_t limit, Tensor& status) {
 }
 
 void embedding(const Tensor& ids, const Tensor& table, Tensor& hidden, const OptTensor& status,
-               const OptTensor& sampled) {
+               const OptTensor& sampled, double scale, const OptTensor& positions, const OptTensor& position_rows) {
   check_cuda(table, "table");
   AKV_CHECK(table.dim() == 2, "table must be [vocab, hidden]");
   const int64_t n = ids.numel(), h = table.size(1);
@@ -115,11 +115,24 @@ void embedding(const Tensor& ids, const Tensor& table, Tensor& hidden, const Opt
     sampled_ptr = sampled->data_ptr<int>();
     num_sampled = sampled->numel();
   }
+  const int* positions_ptr = nullptr;
+  const void* rows_ptr = nullptr;
+  int64_t max_positions = 0;
+  if (position_rows.has_value()) {
+    AKV_CHECK(positions.has_value(), "position_rows needs positions");
+    check_cuda(*position_rows, "position_rows");
+    check_same(*position_rows, table, "position_rows", "table");
+    AKV_CHECK(position_rows->dim() == 2 && position_rows->size(1) == h, "position_rows must be [positions, hidden]");
+    check_i32(*positions, "positions", n);
+    positions_ptr = positions->data_ptr<int>();
+    rows_ptr = position_rows->data_ptr();
+    max_positions = position_rows->size(0);
+  }
   c10::cuda::CUDAGuard guard(table.device());
   check_launch(akv::launch_embedding(ids.data_ptr<int>(), sampled_ptr, num_sampled, table.data_ptr(),
                                      hidden.data_ptr<float>(), n, h,
                                      table.size(0), dtype_code(table, "table"), status_ptr(status),
-                                     stream_of(table)),
+                                     stream_of(table), (float)scale, positions_ptr, rows_ptr, max_positions),
                "embedding");
 }
 
@@ -788,12 +801,16 @@ void scored_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
 void head_prep(const Tensor& x, const OptTensor& slots, Tensor& q_out, const OptTensor& k_cache,
                const OptTensor& v_cache, const OptTensor& v_keep, const OptTensor& v_other,
                const OptTensor& blend_weight, const OptTensor& gate_out, int64_t num_heads, int64_t num_kv_heads,
-               int64_t head_dim, int64_t v_dim, bool unit_norm, double eps, const OptTensor& status) {
+               int64_t head_dim, int64_t v_dim, bool unit_norm, double eps, const OptTensor& status,
+               const OptTensor& q_weight, const OptTensor& k_weight, bool has_kv) {
   check_cuda(x, "x");
   check_cuda(q_out, "q_out");
   check_same(x, q_out, "x", "q_out");
   AKV_CHECK(num_heads > 0 && num_kv_heads > 0 && head_dim > 0 && v_dim > 0, "head_prep: sizes must be positive");
-  const int64_t width = num_heads * head_dim + num_kv_heads * (head_dim + v_dim) + (gate_out.has_value() ? num_heads : 0);
+  AKV_CHECK(has_kv || !(k_cache.has_value() || v_keep.has_value() || v_other.has_value() || k_weight.has_value()),
+            "head_prep: without k and v columns there is nothing to cache, keep, blend or weigh");
+  const int64_t width = num_heads * head_dim + (has_kv ? num_kv_heads * (head_dim + v_dim) : 0) +
+                        (gate_out.has_value() ? num_heads : 0);
   AKV_CHECK(x.dim() == 2 && x.size(1) == width, "x must be [tokens, ", width, "], the q, k, v (and gate) columns");
   const int64_t n = x.size(0);
   AKV_CHECK(q_out.numel() == n * num_heads * head_dim, "q_out must be [tokens, heads * head_dim]");
@@ -844,6 +861,15 @@ void head_prep(const Tensor& x, const OptTensor& slots, Tensor& q_out, const Opt
   p.eps = (float)eps;
   p.dtype = dtype_code(x, "x");
   p.status = status_ptr(status);
+  if (q_weight.has_value()) {
+    check_f32(*q_weight, "q_weight", head_dim);
+    p.q_weight = q_weight->data_ptr<float>();
+  }
+  if (k_weight.has_value()) {
+    check_f32(*k_weight, "k_weight", head_dim);
+    p.k_weight = k_weight->data_ptr<float>();
+  }
+  p.no_kv = has_kv ? 0 : 1;
   c10::cuda::CUDAGuard guard(x.device());
   check_launch(akv::launch_head_prep(p, stream_of(x)), "head_prep");
 }
@@ -931,6 +957,306 @@ void activation(const Tensor& in, Tensor& out, int64_t kind) {
                "activation");
 }
 
+void add_layernorm(Tensor& hidden, const OptTensor& delta, const Tensor& weight, Tensor& out, const OptTensor& rows,
+                   double eps, const OptTensor& status) {
+  check_cuda(hidden, "hidden");
+  AKV_CHECK(hidden.scalar_type() == at::kFloat && hidden.dim() == 2, "hidden must be float32 [tokens, hidden]");
+  const int64_t n = hidden.size(0), h = hidden.size(1);
+  check_f32(weight, "weight", h);
+  check_cuda(out, "out");
+  const int code = dtype_code(out, "out");
+  AKV_CHECK(h * 4 <= 200 * 1024, "add_layernorm: hidden size ", h, " exceeds the kernel's limit of 51200");
+  const void* delta_ptr = nullptr;
+  if (delta.has_value()) {
+    check_cuda(*delta, "delta");
+    check_same(*delta, out, "delta", "out");
+    AKV_CHECK(delta->numel() == n * h, "delta must be [tokens, hidden]");
+    delta_ptr = delta->data_ptr();
+  }
+  const int* rows_ptr = nullptr;
+  int64_t num_rows = 0;
+  if (rows.has_value()) {
+    check_i32(*rows, "rows");
+    rows_ptr = rows->data_ptr<int>();
+    num_rows = rows->numel();
+    AKV_CHECK(out.numel() == num_rows * h, "out must be [rows, hidden]");
+  } else {
+    AKV_CHECK(out.numel() == n * h, "out must be [tokens, hidden]");
+  }
+  c10::cuda::CUDAGuard guard(hidden.device());
+  check_launch(akv::launch_add_layernorm(hidden.data_ptr<float>(), delta_ptr, weight.data_ptr<float>(), out.data_ptr(),
+                                         rows_ptr, num_rows, n, h, (float)eps, code, status_ptr(status),
+                                         stream_of(hidden)),
+               "add_layernorm");
+}
+
+void branch_layernorm(Tensor& hidden, const Tensor& branch, const Tensor& weight, const OptTensor& copy, double eps) {
+  check_cuda(hidden, "hidden");
+  AKV_CHECK(hidden.scalar_type() == at::kFloat && hidden.dim() == 2, "hidden must be float32 [tokens, hidden]");
+  const int64_t n = hidden.size(0), h = hidden.size(1);
+  check_f32(weight, "weight", h);
+  check_cuda(branch, "branch");
+  AKV_CHECK(branch.numel() == n * h && branch.device() == hidden.device(), "branch must be [tokens, hidden]");
+  AKV_CHECK(h * 4 <= 200 * 1024, "branch_layernorm: hidden size ", h, " exceeds the kernel's limit of 51200");
+  void* copy_ptr = nullptr;
+  int copy_code = 0;
+  if (copy.has_value()) {
+    check_cuda(*copy, "copy");
+    AKV_CHECK(copy->scalar_type() == at::kBFloat16 && copy->numel() == n * h && copy->device() == hidden.device(),
+              "copy must be bfloat16 [tokens, hidden]");
+    copy_ptr = copy->data_ptr();
+    copy_code = 1;
+  }
+  c10::cuda::CUDAGuard guard(hidden.device());
+  check_launch(akv::launch_branch_layernorm(hidden.data_ptr<float>(), branch.data_ptr(), dtype_code(branch, "branch"),
+                                            weight.data_ptr<float>(), copy_ptr, copy_code, n, h, (float)eps,
+                                            stream_of(hidden)),
+               "branch_layernorm");
+}
+
+void stream_copy(const Tensor& hidden, Tensor& out) {
+  check_cuda(hidden, "hidden");
+  check_cuda(out, "out");
+  AKV_CHECK(hidden.scalar_type() == at::kFloat && out.scalar_type() == at::kBFloat16 && out.numel() == hidden.numel() &&
+                out.device() == hidden.device(),
+            "stream_copy: float32 in, bfloat16 out of the same size");
+  c10::cuda::CUDAGuard guard(hidden.device());
+  check_launch(akv::launch_stream_copy(hidden.data_ptr<float>(), out.data_ptr(), hidden.numel(), stream_of(hidden)),
+               "stream_copy");
+}
+
+void glu(const Tensor& gate_up, Tensor& out, int64_t kind, int64_t block, double limit, double slope) {
+  check_cuda(gate_up, "gate_up");
+  check_cuda(out, "out");
+  check_same(gate_up, out, "gate_up", "out");
+  AKV_CHECK(gate_up.dim() == 2 && gate_up.size(1) % 2 == 0, "gate_up must be [tokens, 2 * intermediate]");
+  const int64_t n = gate_up.size(0), inter = gate_up.size(1) / 2;
+  AKV_CHECK(out.numel() == n * inter, "out must be [tokens, intermediate]");
+  AKV_CHECK(kind >= 0 && kind <= 2, "glu: kind must be 0 (SiLU), 1 (tanh GELU) or 2 (clamped swish)");
+  AKV_CHECK(kind != 2 || limit > 0, "glu: the clamped form needs a positive limit");
+  if (block == 0) block = inter;
+  AKV_CHECK(block > 0 && inter % block == 0, "glu: block must divide the intermediate size");
+  c10::cuda::CUDAGuard guard(gate_up.device());
+  check_launch(akv::launch_glu(gate_up.data_ptr(), out.data_ptr(), n, inter, block, (int)kind, (float)limit,
+                               (float)slope, dtype_code(gate_up, "gate_up"), stream_of(gate_up)),
+               "glu");
+}
+
+void softcap(Tensor& logits, double cap) {
+  check_cuda(logits, "logits");
+  AKV_CHECK(logits.scalar_type() == at::kFloat, "logits must be float32");
+  AKV_CHECK(cap > 0, "softcap: cap must be positive");
+  c10::cuda::CUDAGuard guard(logits.device());
+  check_launch(akv::launch_softcap(logits.data_ptr<float>(), logits.numel(), (float)cap, stream_of(logits)), "softcap");
+}
+
+akv::DeltaParams delta_params(const Tensor& x, const Tensor& state, const Tensor& cu_q, const Tensor& state_slots,
+                              int64_t num_heads, int64_t num_kv_heads, int64_t head_dim, int64_t v_dim, int64_t taps) {
+  check_cuda(x, "x");
+  AKV_CHECK(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && head_dim > 0 && v_dim > 0,
+            "delta rule: sizes must be positive and heads a multiple of the q/k heads");
+  AKV_CHECK(head_dim <= akv::kDeltaMaxDim && v_dim <= akv::kDeltaMaxDim && akv::delta_scan_supported((int)head_dim, (int)v_dim),
+            "delta rule: a head of ", head_dim, " x ", v_dim, " is outside what the kernels take");
+  AKV_CHECK(taps >= 1 && taps <= akv::kDeltaMaxTaps, "delta rule: taps must be between 1 and ", (int64_t)akv::kDeltaMaxTaps);
+  const int64_t channels = 2 * num_kv_heads * head_dim + num_heads * v_dim;
+  const int64_t width = channels + num_heads * v_dim + 2 * num_heads;
+  AKV_CHECK(x.dim() == 2 && x.size(1) == width, "x must be [tokens, ", width, "]: q, k, v, gate, beta, step");
+  const int64_t memory = num_heads * head_dim * v_dim;
+  check_cuda(state, "state");
+  AKV_CHECK(state.scalar_type() == at::kFloat && state.dim() == 2 && state.size(1) == memory + (taps - 1) * channels &&
+                state.device() == x.device(),
+            "state must be float32 [slots, ", memory + (taps - 1) * channels, "]");
+  check_i32(cu_q, "cu_q", 1);
+  const int64_t num_seqs = cu_q.numel() - 1;
+  check_i32(state_slots, "state_slots", num_seqs);
+  akv::DeltaParams p{};
+  p.x = x.data_ptr();
+  p.state = state.data_ptr<float>();
+  p.cu_q = cu_q.data_ptr<int>();
+  p.state_slots = state_slots.data_ptr<int>();
+  p.num_tokens = x.size(0);
+  p.state_stride = state.size(1);
+  p.memory = memory;
+  p.num_seqs = (int)num_seqs;
+  p.num_slots = (int)state.size(0);
+  p.num_heads = (int)num_heads;
+  p.num_kv_heads = (int)num_kv_heads;
+  p.head_dim = (int)head_dim;
+  p.v_dim = (int)v_dim;
+  p.taps = (int)taps;
+  p.dtype = dtype_code(x, "x");
+  return p;
+}
+
+void delta_prep(const Tensor& x, const Tensor& conv, const Tensor& rate_log, const Tensor& step_bias, const Tensor& state,
+                const Tensor& cu_q, const Tensor& state_slots, Tensor& qkv, Tensor& coef, int64_t num_heads,
+                int64_t num_kv_heads, int64_t head_dim, int64_t v_dim, int64_t taps, double unit_eps) {
+  akv::DeltaParams p = delta_params(x, state, cu_q, state_slots, num_heads, num_kv_heads, head_dim, v_dim, taps);
+  const int64_t channels = 2 * num_kv_heads * head_dim + num_heads * v_dim;
+  check_f32(conv, "conv", channels * taps);
+  check_f32(rate_log, "rate_log", num_heads);
+  check_f32(step_bias, "step_bias", num_heads);
+  check_f32(qkv, "qkv", p.num_tokens * channels);
+  check_f32(coef, "coef", p.num_tokens * 2 * num_heads);
+  p.conv = conv.data_ptr<float>();
+  p.rate_log = rate_log.data_ptr<float>();
+  p.step_bias = step_bias.data_ptr<float>();
+  p.qkv = qkv.data_ptr<float>();
+  p.coef = coef.data_ptr<float>();
+  p.unit_eps = (float)unit_eps;
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_delta_prep(p, stream_of(x)), "delta_prep");
+}
+
+void delta_scan(const Tensor& qkv, const Tensor& coef, const Tensor& x, const Tensor& norm_weight, Tensor& state,
+                const Tensor& cu_q, const Tensor& state_slots, Tensor& scratch, Tensor& out, int64_t num_heads,
+                int64_t num_kv_heads, int64_t head_dim, int64_t v_dim, int64_t taps, double norm_eps) {
+  akv::DeltaParams p = delta_params(x, state, cu_q, state_slots, num_heads, num_kv_heads, head_dim, v_dim, taps);
+  const int64_t channels = 2 * num_kv_heads * head_dim + num_heads * v_dim;
+  check_f32(qkv, "qkv", p.num_tokens * channels);
+  check_f32(coef, "coef", p.num_tokens * 2 * num_heads);
+  check_f32(norm_weight, "norm_weight", v_dim);
+  check_f32(scratch, "scratch", p.num_tokens * num_heads * v_dim);
+  check_cuda(out, "out");
+  check_same(out, x, "out", "x");
+  AKV_CHECK(out.numel() == p.num_tokens * num_heads * v_dim, "out must be [tokens, heads * v_dim]");
+  p.qkv = qkv.data_ptr<float>();
+  p.coef = coef.data_ptr<float>();
+  p.norm_weight = norm_weight.data_ptr<float>();
+  p.scratch = scratch.data_ptr<float>();
+  p.out = out.data_ptr();
+  p.norm_eps = (float)norm_eps;
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_delta_scan(p, stream_of(x)), "delta_scan");
+}
+
+void moe_route(const Tensor& logits, const OptTensor& correction, Tensor& chosen, Tensor& weights, int64_t groups,
+               int64_t keep_groups, int64_t group_top, double scale, double weight_eps) {
+  check_cuda(logits, "logits");
+  AKV_CHECK(logits.scalar_type() == at::kFloat && logits.dim() == 2, "logits must be float32 [tokens, experts]");
+  const int64_t n = logits.size(0), experts = logits.size(1);
+  check_i32(chosen, "chosen");
+  AKV_CHECK(chosen.dim() == 2 && chosen.size(0) == n, "chosen must be [tokens, top]");
+  const int64_t top = chosen.size(1);
+  check_f32(weights, "weights", n * top);
+  AKV_CHECK(experts >= 1 && experts <= akv::kMoeMaxExperts && top >= 1 && top <= 32 && top <= experts,
+            "moe_route: up to ", (int64_t)akv::kMoeMaxExperts, " experts and a top of up to 32");
+  AKV_CHECK(groups >= 1 && experts % groups == 0 && keep_groups >= 1 && keep_groups <= groups && group_top >= 1 &&
+                top <= keep_groups * (experts / groups),
+            "moe_route: the groups must divide the experts and the kept groups hold the top");
+  akv::MoeRouteParams p{};
+  p.logits = logits.data_ptr<float>();
+  if (correction.has_value()) {
+    check_f32(*correction, "correction", experts);
+    p.correction = correction->data_ptr<float>();
+  }
+  p.chosen = chosen.data_ptr<int>();
+  p.weights = weights.data_ptr<float>();
+  p.num_tokens = n;
+  p.experts = (int)experts;
+  p.top = (int)top;
+  p.groups = (int)groups;
+  p.keep_groups = (int)keep_groups;
+  p.group_top = (int)group_top;
+  p.scale = (float)scale;
+  p.weight_eps = (float)weight_eps;
+  c10::cuda::CUDAGuard guard(logits.device());
+  check_launch(akv::launch_moe_route(p, stream_of(logits)), "moe_route");
+}
+
+void moe_sort(const Tensor& chosen, Tensor& order, Tensor& offsets) {
+  check_i32(chosen, "chosen");
+  check_i32(order, "order", chosen.numel());
+  check_i32(offsets, "offsets", 2);
+  const int64_t experts = offsets.numel() - 1;
+  AKV_CHECK(experts <= akv::kMoeMaxExperts, "moe_sort: up to ", (int64_t)akv::kMoeMaxExperts, " experts");
+  c10::cuda::CUDAGuard guard(chosen.device());
+  check_launch(akv::launch_moe_sort(chosen.data_ptr<int>(), order.data_ptr<int>(), offsets.data_ptr<int>(),
+                                    chosen.numel(), (int)experts, stream_of(chosen)),
+               "moe_sort");
+}
+
+void moe_gate_up(const Tensor& x, const Tensor& w, const Tensor& order, const Tensor& offsets, Tensor& act, int64_t top,
+                 double limit, double slope) {
+  check_cuda(x, "x");
+  check_cuda(w, "w");
+  check_cuda(act, "act");
+  check_same(x, w, "x", "w");
+  check_same(x, act, "x", "act");
+  AKV_CHECK(x.dim() == 2 && w.dim() == 3 && w.size(2) == x.size(1) && w.size(1) % 2 == 0,
+            "moe_gate_up: x [tokens, hidden], w [experts, 2 * intermediate, hidden]");
+  const int64_t pairs = order.numel(), experts = w.size(0), inter = w.size(1) / 2;
+  check_i32(order, "order");
+  check_i32(offsets, "offsets", experts + 1);
+  AKV_CHECK(top >= 1 && pairs == x.size(0) * top && act.numel() == pairs * inter && limit > 0,
+            "moe_gate_up: order holds tokens * top pairs, act [pairs, intermediate], a positive limit");
+  akv::MoeGemmParams p{};
+  p.a = x.data_ptr();
+  p.w = w.data_ptr();
+  p.order = order.data_ptr<int>();
+  p.offsets = offsets.data_ptr<int>();
+  p.out = act.data_ptr();
+  p.pairs = pairs;
+  p.experts = (int)experts;
+  p.k = (int)x.size(1);
+  p.n = (int)inter;
+  p.top = (int)top;
+  p.limit = (float)limit;
+  p.slope = (float)slope;
+  p.dtype = dtype_code(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_moe_gemm(p, true, stream_of(x)), "moe_gate_up");
+}
+
+void moe_down(const Tensor& act, const Tensor& w, const Tensor& order, const Tensor& offsets, const Tensor& weights,
+              Tensor& out) {
+  check_cuda(act, "act");
+  check_cuda(w, "w");
+  check_same(act, w, "act", "w");
+  AKV_CHECK(act.dim() == 2 && w.dim() == 3 && w.size(2) == act.size(1), "moe_down: act [pairs, intermediate], w [experts, hidden, intermediate]");
+  const int64_t pairs = act.size(0), experts = w.size(0), hidden = w.size(1);
+  check_i32(order, "order", pairs);
+  check_i32(offsets, "offsets", experts + 1);
+  check_f32(weights, "weights", pairs);
+  check_f32(out, "out", pairs * hidden);
+  AKV_CHECK(order.numel() == pairs, "moe_down: a pair per row of act");
+  akv::MoeGemmParams p{};
+  p.a = act.data_ptr();
+  p.w = w.data_ptr();
+  p.order = order.data_ptr<int>();
+  p.offsets = offsets.data_ptr<int>();
+  p.weights = weights.data_ptr<float>();
+  p.out = out.data_ptr();
+  p.pairs = pairs;
+  p.experts = (int)experts;
+  p.k = (int)act.size(1);
+  p.n = (int)hidden;
+  p.top = 1;
+  p.dtype = dtype_code(act, "act");
+  c10::cuda::CUDAGuard guard(act.device());
+  check_launch(akv::launch_moe_gemm(p, false, stream_of(act)), "moe_down");
+}
+
+void moe_combine(const Tensor& parts, const OptTensor& shared, Tensor& out, int64_t top) {
+  check_cuda(parts, "parts");
+  AKV_CHECK(parts.scalar_type() == at::kFloat && parts.dim() == 2 && top >= 1 && parts.size(0) % top == 0,
+            "moe_combine: parts must be float32 [tokens * top, hidden]");
+  const int64_t n = parts.size(0) / top, h = parts.size(1);
+  check_f32(out, "out", n * h);
+  const void* shared_ptr = nullptr;
+  int shared_code = 0;
+  if (shared.has_value()) {
+    check_cuda(*shared, "shared");
+    AKV_CHECK(shared->numel() == n * h && shared->device() == parts.device(), "shared must be [tokens, hidden]");
+    shared_ptr = shared->data_ptr();
+    shared_code = dtype_code(*shared, "shared");
+  }
+  c10::cuda::CUDAGuard guard(parts.device());
+  check_launch(akv::launch_moe_combine(parts.data_ptr<float>(), shared_ptr, shared_code, out.data_ptr<float>(), n, h,
+                                       (int)top, stream_of(parts)),
+               "moe_combine");
+}
+
 int64_t sample_slices() { return akv::kSampleSlices; }
 
 // parts: float32 workspace of 4 * rows * slices entries (maxima, indices and, as doubles, sums); tickets: int32, at
@@ -968,7 +1294,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wait_selftest", &wait_selftest, py::arg("limit"), py::arg("status"),
         "a bounded wait on a barrier that nothing completes: leaves the wait-timeout code in status");
   m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("hidden"), py::arg("status") = py::none(),
-        py::arg("sampled") = py::none());
+        py::arg("sampled") = py::none(), py::arg("scale") = 1.0, py::arg("positions") = py::none(),
+        py::arg("position_rows") = py::none());
   m.def("add_rmsnorm", &add_rmsnorm, py::arg("hidden"), py::arg("delta"), py::arg("weight"), py::arg("out"),
         py::arg("rows"), py::arg("eps"), py::arg("status") = py::none());
   m.def("silu_mul", &silu_mul, py::arg("gate_up"), py::arg("out"), py::arg("block") = 0);
@@ -1006,13 +1333,37 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("head_prep", &head_prep, py::arg("x"), py::arg("slots"), py::arg("q_out"), py::arg("k_cache"),
         py::arg("v_cache"), py::arg("v_keep"), py::arg("v_other"), py::arg("blend_weight"), py::arg("gate_out"),
         py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("v_dim"), py::arg("unit_norm"),
-        py::arg("eps"), py::arg("status") = py::none());
+        py::arg("eps"), py::arg("status") = py::none(), py::arg("q_weight") = py::none(),
+        py::arg("k_weight") = py::none(), py::arg("has_kv") = true);
   m.def("latent_prep", &latent_prep, py::arg("x"), py::arg("positions"), py::arg("slots"), py::arg("q_weight"),
         py::arg("kv_weight"), py::arg("inv_freq"), py::arg("q_latent"), py::arg("cache"), py::arg("q_rank"),
         py::arg("kv_rank"), py::arg("rot_dim"), py::arg("rotary_dims"), py::arg("eps"), py::arg("status") = py::none());
   m.def("rotate_pairs", &rotate_pairs, py::arg("in"), py::arg("out"), py::arg("positions"), py::arg("inv_freq"),
         py::arg("heads"), py::arg("cols"), py::arg("rotary_dims"), py::arg("in_offset"), py::arg("out_offset"));
   m.def("activation", &activation, py::arg("in"), py::arg("out"), py::arg("kind"));
+  m.def("add_layernorm", &add_layernorm, py::arg("hidden"), py::arg("delta"), py::arg("weight"), py::arg("out"),
+        py::arg("rows"), py::arg("eps"), py::arg("status") = py::none());
+  m.def("branch_layernorm", &branch_layernorm, py::arg("hidden"), py::arg("branch"), py::arg("weight"), py::arg("copy"),
+        py::arg("eps"));
+  m.def("stream_copy", &stream_copy, py::arg("hidden"), py::arg("out"));
+  m.def("glu", &glu, py::arg("gate_up"), py::arg("out"), py::arg("kind"), py::arg("block") = 0, py::arg("limit") = 0.0,
+        py::arg("slope") = 1.0);
+  m.def("softcap", &softcap, py::arg("logits"), py::arg("cap"));
+  m.def("delta_prep", &delta_prep, py::arg("x"), py::arg("conv"), py::arg("rate_log"), py::arg("step_bias"),
+        py::arg("state"), py::arg("cu_q"), py::arg("state_slots"), py::arg("qkv"), py::arg("coef"), py::arg("num_heads"),
+        py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("v_dim"), py::arg("taps"), py::arg("unit_eps"));
+  m.def("delta_scan", &delta_scan, py::arg("qkv"), py::arg("coef"), py::arg("x"), py::arg("norm_weight"), py::arg("state"),
+        py::arg("cu_q"), py::arg("state_slots"), py::arg("scratch"), py::arg("out"), py::arg("num_heads"),
+        py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("v_dim"), py::arg("taps"), py::arg("norm_eps"));
+  m.def("delta_scan_supported", [](int64_t dim, int64_t v_dim) { return akv::delta_scan_supported((int)dim, (int)v_dim); });
+  m.def("moe_route", &moe_route, py::arg("logits"), py::arg("correction"), py::arg("chosen"), py::arg("weights"),
+        py::arg("groups"), py::arg("keep_groups"), py::arg("group_top"), py::arg("scale"), py::arg("weight_eps"));
+  m.def("moe_sort", &moe_sort, py::arg("chosen"), py::arg("order"), py::arg("offsets"));
+  m.def("moe_gate_up", &moe_gate_up, py::arg("x"), py::arg("w"), py::arg("order"), py::arg("offsets"), py::arg("act"),
+        py::arg("top"), py::arg("limit"), py::arg("slope"));
+  m.def("moe_down", &moe_down, py::arg("act"), py::arg("w"), py::arg("order"), py::arg("offsets"), py::arg("weights"),
+        py::arg("out"));
+  m.def("moe_combine", &moe_combine, py::arg("parts"), py::arg("shared"), py::arg("out"), py::arg("top"));
   m.def("paged_attention", &paged_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"),
         py::arg("block_table"), py::arg("cu_q"), py::arg("ctx_lens"), py::arg("tile_seq"), py::arg("tile_q0"),
         py::arg("tile_nq"), py::arg("partials"), py::arg("num_tiles"), py::arg("q_tile"), py::arg("num_splits"),

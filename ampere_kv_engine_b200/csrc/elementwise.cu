@@ -75,7 +75,9 @@ int launch_smoke_add(const float* a, const float* b, float* out, int64_t n, cuda
 template <typename T>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ sampled,
                                  int64_t num_sampled, const T* __restrict__ table, float* __restrict__ hidden,
-                                 int64_t hidden_size, int64_t vocab, int* status) {
+                                 int64_t hidden_size, int64_t vocab, float scale,
+                                 const int32_t* __restrict__ positions, const T* __restrict__ position_rows,
+                                 int64_t max_positions, int* status) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t token = blockIdx.x;
@@ -88,21 +90,38 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const int32_t*
   }
   const T* row = table + id * hidden_size;
   float* dst = hidden + token * hidden_size;
-  for (int64_t i = threadIdx.x; i < hidden_size; i += blockDim.x) dst[i] = to_float<T>(row[i]);
+  if (position_rows == nullptr) {
+    if (scale == 1.f) {
+      for (int64_t i = threadIdx.x; i < hidden_size; i += blockDim.x) dst[i] = to_float<T>(row[i]);
+    } else {
+      for (int64_t i = threadIdx.x; i < hidden_size; i += blockDim.x) dst[i] = to_float<T>(row[i]) * scale;
+    }
+    return;
+  }
+  // a learned row per position, added unscaled
+  int64_t position = positions[token];
+  if (position < 0 || position >= max_positions) {
+    if (threadIdx.x == 0) set_status(status, kBadRow);
+    position = 0;
+  }
+  const T* at = position_rows + position * hidden_size;
+  for (int64_t i = threadIdx.x; i < hidden_size; i += blockDim.x)
+    dst[i] = to_float<T>(row[i]) * scale + to_float<T>(at[i]);
 }
 
 int launch_embedding(const int32_t* ids, const int32_t* sampled, int64_t num_sampled, const void* table,
                      float* hidden, int64_t num_tokens, int64_t hidden_size, int64_t vocab, int dtype, int* status,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, float scale, const int32_t* positions, const void* position_rows,
+                     int64_t max_positions) {
   if (num_tokens == 0) return 0;
   const int threads = (int)(hidden_size >= 1024 ? 256 : (hidden_size >= 128 ? 128 : 32));
   if (dtype == kBFloat16)
     return (int)launch_chain(embedding_kernel<__nv_bfloat16>, dim3((unsigned)num_tokens), dim3(threads), 0, stream,
                              dim3(1, 1, 1), ids, sampled, num_sampled, (const __nv_bfloat16*)table, hidden, hidden_size,
-                             vocab, status);
+                             vocab, scale, positions, (const __nv_bfloat16*)position_rows, max_positions, status);
   return (int)launch_chain(embedding_kernel<float>, dim3((unsigned)num_tokens), dim3(threads), 0, stream,
                            dim3(1, 1, 1), ids, sampled, num_sampled, (const float*)table, hidden, hidden_size, vocab,
-                           status);
+                           scale, positions, (const float*)position_rows, max_positions, status);
 }
 
 // ---------------------------------------------------------------------------------------------------------

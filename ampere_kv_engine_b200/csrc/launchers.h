@@ -23,11 +23,36 @@ int launch_wait_selftest(uint32_t limit, int* status, cudaStream_t stream);
 
 int launch_smoke_add(const float* a, const float* b, float* out, int64_t n, cudaStream_t stream);
 
-// hidden[n, :] = float(table[ids[n], :]).  With `sampled` (may be null), an id of -(r + 1) stands for sampled[r]:
-// the token the previous step chose in its row r, still on the device.
+// hidden[n, :] = float(table[ids[n], :]) * scale (+ float(position_rows[positions[n], :]) when a position table is
+// given).  With `sampled` (may be null), an id of -(r + 1) stands for sampled[r]: the token the previous step chose
+// in its row r, still on the device.
 int launch_embedding(const int32_t* ids, const int32_t* sampled, int64_t num_sampled, const void* table,
                      float* hidden, int64_t num_tokens, int64_t hidden_size, int64_t vocab, int dtype, int* status,
-                     cudaStream_t stream);
+                     cudaStream_t stream, float scale = 1.f, const int32_t* positions = nullptr,
+                     const void* position_rows = nullptr, int64_t max_positions = 0);
+
+// hidden += delta (if delta; same dtype as out); out = (x - mean) / sqrt(var + eps) * weight of every row, the
+// variance being the mean of the squared deviations.  With `rows` only those rows are read and hidden is untouched.
+int launch_add_layernorm(float* hidden, const void* delta, const float* weight, void* out, const int32_t* rows,
+                         int64_t num_rows, int64_t num_tokens, int64_t hidden_size, float eps, int dtype, int* status,
+                         cudaStream_t stream);
+
+// hidden += LayerNorm(branch) * weight, row by row; `copy` (bfloat16 or null) receives the new hidden rounded.
+int launch_branch_layernorm(float* hidden, const void* branch, int branch_dtype, const float* weight, void* copy,
+                            int copy_dtype, int64_t num_tokens, int64_t hidden_size, float eps, cudaStream_t stream);
+
+// out (bfloat16) = in (float32), element by element.
+int launch_stream_copy(const float* in, void* out, int64_t total, cudaStream_t stream);
+
+// out[n, i] = act(gate(n, i)) * up(n, i) over gate_up [tokens, 2 inter] whose gate and up columns alternate in runs
+// of `block` columns.  kGluClampedSwish: g = min(gate, limit), u = clamp(up, -limit, limit),
+// g * sigmoid(slope * g) * (u + 1).
+enum Glu : int { kGluSilu = 0, kGluGeluTanh = 1, kGluClampedSwish = 2 };
+int launch_glu(const void* gate_up, void* out, int64_t num_tokens, int64_t inter, int64_t block, int kind, float limit,
+               float slope, int dtype, cudaStream_t stream);
+
+// x = cap * tanh(x / cap) in place.
+int launch_softcap(float* x, int64_t total, float cap, cudaStream_t stream);
 
 // hidden += delta (if delta); out = rmsnorm(hidden) * weight.  With `rows` (num_rows entries)
 // only those rows are read, hidden is left untouched and out is [num_rows, hidden_size].
@@ -237,6 +262,9 @@ struct HeadPrepParams {
   float eps;
   int dtype;
   int* status;
+  const float* q_weight;       // [D] or null: q heads are multiplied by it after the norm
+  const float* k_weight;       // [D] or null: likewise for k heads
+  int no_kv;                   // 1: x holds no k and v columns (the mixer reads another position's pages)
 };
 int launch_head_prep(const HeadPrepParams& p, cudaStream_t stream);
 
@@ -267,6 +295,66 @@ int launch_latent_prep(const LatentPrepParams& p, cudaStream_t stream);
 int launch_rotate_pairs(const void* in, void* out, const int32_t* positions, const float* inv_freq,
                         int64_t num_tokens, int heads, int cols, int rotary_dims, int64_t in_width, int in_offset,
                         int64_t out_width, int out_offset, int dtype, cudaStream_t stream);
+
+// The gated delta rule (delta_rule.cu).  x [N, q | k | v | gate | beta | step] with num_kv_heads heads of head_dim
+// for q and k, num_heads heads of v_dim for v and gate, one column per head for beta and step.  state
+// [num_slots, state_stride] float32: per slot heads * v_dim * head_dim floats of S ([head][value column][dim]) at
+// offset 0 and (taps - 1) * channels convolution inputs at offset `memory`.
+constexpr int kDeltaMaxDim = 256;
+constexpr int kDeltaMaxTaps = 8;
+struct DeltaParams {
+  const void* x;
+  const float* conv;           // [channels, taps], channels = 2 * num_kv_heads * head_dim + num_heads * v_dim
+  const float* rate_log;       // [num_heads]
+  const float* step_bias;      // [num_heads]
+  const float* norm_weight;    // [v_dim]
+  float* state;
+  const int32_t* cu_q;         // [num_seqs + 1]
+  const int32_t* state_slots;  // [num_seqs]; negative: the sequence is padding
+  float* qkv;                  // [N, channels]: unit q, unit k, v
+  float* coef;                 // [N, 2 * num_heads]: beta, decay
+  float* scratch;              // [N, num_heads * v_dim]: o before its norm
+  void* out;                   // [N, num_heads * v_dim]
+  int64_t num_tokens, state_stride, memory;
+  int num_seqs, num_slots, num_heads, num_kv_heads, head_dim, v_dim, taps;
+  float unit_eps, norm_eps;
+  int dtype;
+};
+int launch_delta_prep(const DeltaParams& p, cudaStream_t stream);
+int launch_delta_scan(const DeltaParams& p, cudaStream_t stream);
+bool delta_scan_supported(int dim, int v_dim);
+
+// Routed experts (routed_experts.cu).
+constexpr int kMoeMaxExperts = 512;
+struct MoeRouteParams {
+  const float* logits;         // [N, experts]
+  const float* correction;     // [experts] or null: added to the scores for the choice only
+  int32_t* chosen;             // [N, top]
+  float* weights;              // [N, top]
+  int64_t num_tokens;
+  int experts, top, groups, keep_groups, group_top;
+  float scale, weight_eps;
+};
+int launch_moe_route(const MoeRouteParams& p, cudaStream_t stream);
+// order [pairs]: the (token, choice) pairs (token * top + choice) sorted by expert; offsets [experts + 1].
+int launch_moe_sort(const int32_t* chosen, int32_t* order, int32_t* offsets, int64_t pairs, int experts,
+                    cudaStream_t stream);
+struct MoeGemmParams {
+  const void* a;               // gated: x [tokens, k]; else the activations [pairs, k] in sorted order
+  const void* w;               // gated: [experts, 2 n, k] (gate rows, then up rows); else [experts, n, k]
+  const int32_t* order;        // [pairs]
+  const int32_t* offsets;      // [experts + 1]
+  const float* weights;        // [pairs] by pair (not gated)
+  void* out;                   // gated: [pairs, n] in sorted order, type of a; else float32 [pairs, n] by pair
+  int64_t pairs;
+  int experts, k, n, top;
+  float limit, slope;
+  int dtype;
+};
+int launch_moe_gemm(const MoeGemmParams& p, bool gated, cudaStream_t stream);
+// out[t] = sum over c < top of parts[t * top + c] (+ shared[t]), float32.
+int launch_moe_combine(const float* parts, const void* shared, int shared_dtype, float* out, int64_t num_tokens,
+                       int64_t width, int top, cudaStream_t stream);
 
 enum Activation : int { kActReluSquared = 0, kActGeluTanh = 1, kActSilu = 2 };
 int launch_activation(const void* in, void* out, int64_t total, int kind, int dtype, cudaStream_t stream);

@@ -40,12 +40,12 @@ __global__ void head_prep_kernel(HeadPrepParams p) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
-  const int units = p.num_heads + 2 * p.num_kv_heads + (p.gate_out != nullptr ? 1 : 0);
+  const int NH = p.num_heads, NKV = p.no_kv ? 0 : p.num_kv_heads, D = p.head_dim, DV = p.v_dim;
+  const int units = NH + 2 * NKV + (p.gate_out != nullptr ? 1 : 0);
   const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= p.num_tokens * units) return;
   const int64_t token = item / units;
   const int unit = (int)(item - token * units);
-  const int NH = p.num_heads, NKV = p.num_kv_heads, D = p.head_dim, DV = p.v_dim;
   const int64_t width = (int64_t)NH * D + (int64_t)NKV * D + (int64_t)NKV * DV + (p.gate_out != nullptr ? NH : 0);
   const T* x = (const T*)p.x + token * width;
   const int slot = p.slots != nullptr ? p.slots[token] : -1;
@@ -68,7 +68,12 @@ __global__ void head_prep_kernel(HeadPrepParams p) {
                                  : nullptr;
     }
     if (dst == nullptr) return;
-    for (int d = lane; d < D; d += 32) dst[d] = from_float<T>(to_float<T>(src[d]) * inv);
+    const float* w = is_q ? p.q_weight : p.k_weight;
+    if (w != nullptr) {
+      for (int d = lane; d < D; d += 32) dst[d] = from_float<T>(to_float<T>(src[d]) * inv * w[d]);
+    } else {
+      for (int d = lane; d < D; d += 32) dst[d] = from_float<T>(to_float<T>(src[d]) * inv);
+    }
     return;
   }
   if (unit < NH + 2 * NKV) {
@@ -93,7 +98,7 @@ __global__ void head_prep_kernel(HeadPrepParams p) {
 
 int launch_head_prep(const HeadPrepParams& p, cudaStream_t stream) {
   if (p.num_tokens == 0) return 0;
-  const int units = p.num_heads + 2 * p.num_kv_heads + (p.gate_out != nullptr ? 1 : 0);
+  const int units = p.num_heads + (p.no_kv ? 0 : 2 * p.num_kv_heads) + (p.gate_out != nullptr ? 1 : 0);
   const int warps = 4;
   const int64_t blocks = (p.num_tokens * units + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;

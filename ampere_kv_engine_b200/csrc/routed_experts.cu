@@ -1,0 +1,341 @@
+// A feed-forward of routed experts, entirely on the device (no host read of the routing).
+//
+//   moe_route:    per token: s = sigmoid(logits); choice = s + correction; the experts form equal groups of
+//                 neighbours, a group's score is the sum of its group_top largest choice scores, only experts of the
+//                 keep best groups can be chosen; the top largest remaining choice scores are chosen (ties: the lower
+//                 index); weights = chosen s / (their sum + eps) * scale.  One warp per token, all in float.
+//   moe_sort:     a counting sort of the (token, choice) pairs by expert: where each expert's run begins, and the
+//                 pairs in that order (within an expert in no particular order: every row is computed by itself).
+//   moe_gate_up:  for the sorted rows of every expert, both products with the expert's matrices and the clamped
+//                 activation on the output tile.
+//   moe_down:     the third product, times the pair's weight, written to the pair's own row (float32).
+//   moe_combine:  a token's rows added up in the order of its choices, plus the shared expert's row.
+//
+// The grouped products tile the sorted rows expert by expert: a block finds its (expert, row tile) by walking the
+// run starts, so the grid depends on the batch layout alone.  Each output element is one dot product accumulated
+// in float in the order of k, whatever tile it falls in: a row's result does not depend on the rest of the batch.
+#include "common.cuh"
+#include "launchers.h"
+
+#include <float.h>
+
+namespace akv {
+
+namespace {
+
+constexpr int kRouteWarps = 4;
+
+__device__ __forceinline__ bool better(float v, int i, float best, int best_i) {
+  return v > best || (v == best && i < best_i);
+}
+
+}  // namespace
+
+__global__ void moe_route_kernel(MoeRouteParams p) {
+  extern __shared__ float route_smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t token = (int64_t)blockIdx.x * kRouteWarps + warp;
+  if (token >= p.num_tokens) return;
+  const int E = p.experts, groups = p.groups, per = E / groups;
+  float* score = route_smem + (size_t)warp * (2 * E + 2 * groups);     // s
+  float* choice = score + E;                                            // s + correction, later masked
+  float* group_score = choice + E;
+  float* group_kept = group_score + groups;
+  const float* z = p.logits + token * E;
+  for (int e = lane; e < E; e += 32) {
+    const float s = 1.f / (1.f + expf(-z[e]));
+    float c = p.correction != nullptr ? s + p.correction[e] : s;
+    if (!(c == c)) c = -FLT_MAX;          // a row of padding may hold anything; the choice must still be an expert
+    score[e] = s;
+    choice[e] = c;
+  }
+  __syncwarp();
+  if (groups > 1) {
+    const int take = min(p.group_top, per);
+    for (int g = lane; g < groups; g += 32) {
+      // the sum of the group's `take` largest choice scores: repeated maximum, skipping what was taken
+      const float* c = choice + g * per;
+      float sum = 0.f;
+      float last = FLT_MAX;
+      int last_i = -1;
+      for (int r = 0; r < take; ++r) {
+        float best = -FLT_MAX;
+        int best_i = -1;
+        for (int i = 0; i < per; ++i) {
+          // candidates: everything after (last, last_i) in the order (value descending, index ascending)
+          const bool after = c[i] < last || (c[i] == last && i > last_i);
+          if (after && (best_i < 0 || better(c[i], i, best, best_i))) {
+            best = c[i];
+            best_i = i;
+          }
+        }
+        if (best_i < 0) break;
+        sum += best;
+        last = best;
+        last_i = best_i;
+      }
+      group_score[g] = sum;
+    }
+    __syncwarp();
+    for (int g = lane; g < groups; g += 32) {
+      int rank = 0;
+      for (int o = 0; o < groups; ++o)
+        rank += (group_score[o] > group_score[g] || (group_score[o] == group_score[g] && o < g)) ? 1 : 0;
+      group_kept[g] = rank < p.keep_groups ? 1.f : 0.f;
+    }
+    __syncwarp();
+    for (int e = lane; e < E; e += 32)
+      if (group_kept[e / per] == 0.f) choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  // the `top` largest choice scores, one after the other
+  float picked_sum = 0.f;
+  float my_score = 0.f;           // lane r keeps the r-th choice
+  int my_expert = 0;
+  for (int r = 0; r < p.top; ++r) {
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float c = choice[e];
+      if (c != c) continue;       // marks of what was chosen already
+      if (better(c, e, best, best_i) || best_i == 0x7fffffff) {
+        best = c;
+        best_i = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_i = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (other_i != 0x7fffffff && (best_i == 0x7fffffff || better(other, other_i, best, best_i))) {
+        best = other;
+        best_i = other_i;
+      }
+    }
+    if (best_i == 0x7fffffff) best_i = 0;       // more choices than experts: cannot happen with a checked config
+    const float s = score[best_i];
+    picked_sum += s;
+    if (lane == r % 32) {
+      my_score = s;
+      my_expert = best_i;
+    }
+    if (lane == 0) choice[best_i] = __int_as_float(0x7fc00000);   // NaN: taken
+    __syncwarp();
+  }
+  if (lane < p.top) {          // top <= 32 (checked by the launcher)
+    p.chosen[token * p.top + lane] = my_expert;
+    p.weights[token * p.top + lane] = my_score / (picked_sum + p.weight_eps) * p.scale;
+  }
+}
+
+int launch_moe_route(const MoeRouteParams& p, cudaStream_t stream) {
+  if (p.num_tokens == 0) return 0;
+  if (p.experts <= 0 || p.experts > kMoeMaxExperts || p.top <= 0 || p.top > 32 || p.top > p.experts || p.groups <= 0 ||
+      p.experts % p.groups || p.keep_groups <= 0 || p.keep_groups > p.groups || p.group_top <= 0)
+    return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)kRouteWarps * (2 * p.experts + 2 * p.groups) * sizeof(float);
+  const int64_t blocks = (p.num_tokens + kRouteWarps - 1) / kRouteWarps;
+  if (blocks > 0x7fffffffLL || smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+  return (int)launch_chain(moe_route_kernel, dim3((unsigned)blocks), dim3(kRouteWarps * 32), smem, stream, dim3(1, 1, 1), p);
+}
+
+// One block: counts per expert in shared memory, their running sum, then every pair takes the next place of its
+// expert's run.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t* __restrict__ chosen, int32_t* __restrict__ order,
+                                                        int32_t* __restrict__ offsets, int64_t pairs, int experts) {
+  __shared__ int counts[kMoeMaxExperts];
+  __shared__ int starts[kMoeMaxExperts + 1];
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int64_t i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = min(max(chosen[i], 0), experts - 1);
+    atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < experts; ++e) {
+      starts[e] = run;
+      run += counts[e];
+    }
+    starts[experts] = run;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = starts[e];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int64_t i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = min(max(chosen[i], 0), experts - 1);
+    order[starts[e] + atomicAdd(&counts[e], 1)] = (int32_t)i;
+  }
+}
+
+int launch_moe_sort(const int32_t* chosen, int32_t* order, int32_t* offsets, int64_t pairs, int experts,
+                    cudaStream_t stream) {
+  if (experts <= 0 || experts > kMoeMaxExperts || pairs > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  return (int)launch_chain(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, dim3(1, 1, 1), chosen, order, offsets, pairs,
+                           experts);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// The grouped products.  A block computes kTileRows sorted rows of one expert times kTileCols output features (of
+// the gate and the up matrix at once in the first product), K in steps of kTileK through shared memory (operands
+// widened to float there), 2 x 4 outputs per thread.
+namespace {
+constexpr int kTileRows = 32, kTileCols = 64, kTileK = 32, kGemmThreads = 256;
+
+// the (expert, first sorted row, rows) of row tile `tile`, or rows = 0 when the batch has fewer tiles
+__device__ __forceinline__ void find_tile(const int32_t* offsets, int experts, int tile, int& expert, int& row0,
+                                          int& rows) {
+  rows = 0;
+  expert = row0 = 0;
+  int seen = 0;
+  for (int e = 0; e < experts; ++e) {
+    const int begin = offsets[e], count = offsets[e + 1] - begin;
+    const int tiles = (count + kTileRows - 1) / kTileRows;
+    if (tile < seen + tiles) {
+      expert = e;
+      row0 = begin + (tile - seen) * kTileRows;
+      rows = min(kTileRows, begin + count - row0);
+      return;
+    }
+    seen += tiles;
+  }
+}
+}  // namespace
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(kGemmThreads) moe_gemm_kernel(MoeGemmParams p) {
+  __shared__ float a_tile[kTileK][kTileRows + 1];
+  __shared__ float w_tile[GATED ? 2 : 1][kTileK][kTileCols + 1];
+  __shared__ int tile_info[3];
+  __shared__ int64_t row_source[kTileRows];
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    int e, r0, n;
+    find_tile(p.offsets, p.experts, blockIdx.y, e, r0, n);
+    tile_info[0] = e;
+    tile_info[1] = r0;
+    tile_info[2] = n;
+  }
+  __syncthreads();
+  const int expert = tile_info[0], row0 = tile_info[1], rows = tile_info[2];
+  if (rows == 0) return;
+  const int K = p.k, N = p.n;                       // N: output features (per matrix in the gated product)
+  const int col0 = blockIdx.x * kTileCols;
+  if (threadIdx.x < kTileRows) {
+    const int r = threadIdx.x;
+    int64_t src = -1;
+    if (r < rows) src = GATED ? (int64_t)(p.order[row0 + r] / p.top) : (int64_t)(row0 + r);
+    row_source[r] = src;
+  }
+  __syncthreads();
+  const T* a = (const T*)p.a;
+  const T* w = (const T*)p.w + (int64_t)expert * (GATED ? 2 : 1) * N * K;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  float acc[GATED ? 2 : 1][2][4] = {};
+  for (int k0 = 0; k0 < K; k0 += kTileK) {
+    for (int i = threadIdx.x; i < kTileRows * kTileK; i += kGemmThreads) {
+      const int r = i / kTileK, kk = i % kTileK;
+      const int64_t src = row_source[r];
+      a_tile[kk][r] = (src >= 0 && k0 + kk < K) ? to_float<T>(a[src * K + k0 + kk]) : 0.f;
+    }
+    for (int i = threadIdx.x; i < kTileCols * kTileK; i += kGemmThreads) {
+      const int c = i / kTileK, kk = i % kTileK;
+      const bool inside = col0 + c < N && k0 + kk < K;
+      w_tile[0][kk][c] = inside ? to_float<T>(w[(int64_t)(col0 + c) * K + k0 + kk]) : 0.f;
+      if (GATED) w_tile[1][kk][c] = inside ? to_float<T>(w[(int64_t)(N + col0 + c) * K + k0 + kk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < kTileK; ++kk) {
+      const float a0 = a_tile[kk][ty * 2], a1 = a_tile[kk][ty * 2 + 1];
+#pragma unroll
+      for (int m = 0; m < (GATED ? 2 : 1); ++m) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float b = w_tile[m][kk][tx * 4 + j];
+          acc[m][0][j] = fmaf(a0, b, acc[m][0][j]);
+          acc[m][1][j] = fmaf(a1, b, acc[m][1][j]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = ty * 2 + i;
+    if (r >= rows) continue;
+    if (GATED) {
+      T* dst = (T*)p.out + (int64_t)(row0 + r) * N;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = col0 + tx * 4 + j;
+        if (c >= N) continue;
+        const float g = fminf(acc[0][i][j], p.limit);
+        const float u = fminf(fmaxf(acc[GATED ? 1 : 0][i][j], -p.limit), p.limit);
+        dst[c] = from_float<T>(g / (1.f + expf(-p.slope * g)) * (u + 1.f));
+      }
+    } else {
+      const int pair = p.order[row0 + r];
+      const float weight = p.weights[pair];
+      float* dst = (float*)p.out + (int64_t)pair * N;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = col0 + tx * 4 + j;
+        if (c < N) dst[c] = weight * acc[0][i][j];
+      }
+    }
+  }
+}
+
+int launch_moe_gemm(const MoeGemmParams& p, bool gated, cudaStream_t stream) {
+  if (p.pairs == 0) return 0;
+  if (p.experts <= 0 || p.experts > kMoeMaxExperts || p.k <= 0 || p.n <= 0 || p.top <= 0) return (int)cudaErrorInvalidValue;
+  // every expert may end in a tile that is not full
+  const int64_t row_tiles = p.pairs / kTileRows + (p.pairs < p.experts ? p.pairs : p.experts);
+  const int64_t col_tiles = (p.n + kTileCols - 1) / kTileCols;
+  if (row_tiles > 65535 || col_tiles > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  const dim3 grid((unsigned)col_tiles, (unsigned)row_tiles);
+  if (p.dtype == kBFloat16) {
+    if (gated) return (int)launch_chain(moe_gemm_kernel<__nv_bfloat16, true>, grid, dim3(kGemmThreads), 0, stream, dim3(1, 1, 1), p);
+    return (int)launch_chain(moe_gemm_kernel<__nv_bfloat16, false>, grid, dim3(kGemmThreads), 0, stream, dim3(1, 1, 1), p);
+  }
+  if (gated) return (int)launch_chain(moe_gemm_kernel<float, true>, grid, dim3(kGemmThreads), 0, stream, dim3(1, 1, 1), p);
+  return (int)launch_chain(moe_gemm_kernel<float, false>, grid, dim3(kGemmThreads), 0, stream, dim3(1, 1, 1), p);
+}
+
+template <typename TS>
+__global__ void moe_combine_kernel(const float* __restrict__ parts, const TS* __restrict__ shared,
+                                   float* __restrict__ out, int64_t total, int64_t width, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int64_t token = idx / width, c = idx - token * width;
+  float sum = 0.f;
+  for (int s = 0; s < top; ++s) sum += parts[(token * top + s) * width + c];
+  if (shared != nullptr) sum += to_float<TS>(shared[idx]);
+  out[idx] = sum;
+}
+
+int launch_moe_combine(const float* parts, const void* shared, int shared_dtype, float* out, int64_t num_tokens,
+                       int64_t width, int top, cudaStream_t stream) {
+  const int64_t total = num_tokens * width;
+  if (total == 0) return 0;
+  const int threads = 256;
+  const int64_t blocks = (total + threads - 1) / threads;
+  if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  if (shared != nullptr && shared_dtype == kBFloat16)
+    return (int)launch_chain(moe_combine_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream,
+                             dim3(1, 1, 1), parts, (const __nv_bfloat16*)shared, out, total, width, top);
+  return (int)launch_chain(moe_combine_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, dim3(1, 1, 1),
+                           parts, (const float*)shared, out, total, width, top);
+}
+
+}  // namespace akv

@@ -48,7 +48,7 @@ class StepContext:
     positions: torch.Tensor         # [tokens] int32, absolute
     cu_q: torch.Tensor              # [sequences + 1] int32: first batch row of each sequence
     ctx_lens: torch.Tensor          # [sequences] int32: sequence length once this step's tokens are in
-    state_slots: torch.Tensor       # [sequences] int32
+    state_slots: torch.Tensor       # [sequences] int32 (-1: a padded sequence of a captured step)
     logit_rows: torch.Tensor        # [wanted] int32 batch rows
     num_logit_rows: int
     tile_seq: torch.Tensor          # attention query tiles: sequence, first batch row, rows
@@ -136,7 +136,7 @@ def fill_host(manager: CacheManager, entries: list[SeqStep], layout: BatchLayout
     put(2, cu)
     host[off[3]:off[3] + layout.num_seqs] = 1
     put(3, ctx_lens)
-    host[off[4]:off[4] + layout.num_seqs] = 0
+    host[off[4]:off[4] + layout.num_seqs] = -1      # a padded sequence has no state: kernels leave it alone
     put(4, [e.seq.state_slot for e in entries])
     host[off[5]:off[5] + max(1, layout.num_logit_rows)] = 0
     put(5, [int(cu[s]) + w for s, e in enumerate(entries) for w in e.want])

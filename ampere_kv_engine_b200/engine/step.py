@@ -172,7 +172,7 @@ class ModelRunner:
         dev.copy_(pinned, non_blocking=False)
         # the split count of the attention kernels is fixed at capture: size it for the middle of the contexts that
         # this bucket of table widths serves (any count is right for any context; it only decides the speed)
-        max_context = max(1, (max(layout.widths) - _WIDTH_STEP // 2) * self.manager.page_size)
+        max_context = max(1, (max(layout.widths, default=1) - _WIDTH_STEP // 2) * self.manager.page_size)
         # and for the mix of lengths this batch has (the next batches of the bucket are mostly this one, grown)
         live = [c for c in ctx_lens if c > 0] or [max_context]
         mean_context = max(1, max_context * sum(live) // (len(live) * max(live)))
@@ -181,8 +181,14 @@ class ModelRunner:
                            h2d_bytes=int(layout.total * 4), sampled=self.sampled,
                            decode_contexts=(max_context, mean_context))
         # one eager run first (library handles and workspaces come into being outside the capture); it writes the
-        # same cache slots the captured run writes again
+        # same cache slots the captured run writes again.  A mixer's state is not a slot that can be written twice:
+        # what the requests' state slots held is put back before the step runs for good.
+        slots = torch.tensor([e.seq.state_slot for e in entries], dtype=torch.long, device=self.device)
+        kept = [None if state is None else state[slots].clone() for state in self.manager.state]
         self.model.forward(ctx, self.views)
+        for state, before in zip(self.manager.state, kept):
+            if state is not None:
+                state[slots] = before
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count

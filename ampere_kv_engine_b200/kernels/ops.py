@@ -43,13 +43,26 @@ def smoke_add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor | None = None,
-              sampled: torch.Tensor | None = None) -> torch.Tensor:
-    """float32 residual stream [tokens, hidden] gathered from ``table`` rows.  With ``sampled`` (int32, on the
-    device) an id of ``-(r + 1)`` stands for ``sampled[r]``: the token the previous step chose in its row r."""
+              sampled: torch.Tensor | None = None, scale: float = 1.0, positions: torch.Tensor | None = None,
+              position_rows: torch.Tensor | None = None) -> torch.Tensor:
+    """float32 residual stream [tokens, hidden] gathered from ``table`` rows, times ``scale``, plus (with
+    ``position_rows`` [max positions, hidden] and ``positions``) the row of each token's position.  With
+    ``sampled`` (int32, on the device) an id of ``-(r + 1)`` stands for ``sampled[r]``: the token the previous step
+    chose in its row r."""
     hidden = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
-    ext().embedding(ids, table, hidden, status, sampled)
+    if scale == 1.0 and position_rows is None:
+        ext().embedding(ids, table, hidden, status, sampled)
+    else:
+        ext().embedding(ids, table, hidden, status, sampled, float(scale), positions, position_rows)
     _launched()
     return hidden
+
+
+def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """``cap * tanh(logits / cap)`` in place on float32 logits."""
+    ext().softcap(logits, float(cap))
+    _launched()
+    return logits
 
 
 def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
@@ -63,6 +76,61 @@ def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.
     n = hidden.shape[0] if rows is None else rows.numel()
     out = torch.empty((n, hidden.shape[1]), dtype=out_dtype, device=hidden.device)
     ext().add_rmsnorm(hidden, delta, weight, out, rows, float(eps), status)
+    _launched()
+    return out
+
+
+def add_layernorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                  out_dtype: torch.dtype, rows: torch.Tensor | None = None,
+                  status: torch.Tensor | None = None) -> torch.Tensor:
+    """``hidden += delta`` in place (whole-batch form), then ``(x - mean) / sqrt(var + eps) * weight`` of every row
+    (the variance is the mean of the squared deviations).  With ``rows`` only those rows are normalised and
+    ``hidden`` is left as it is."""
+    n = hidden.shape[0] if rows is None else rows.numel()
+    out = torch.empty((n, hidden.shape[1]), dtype=out_dtype, device=hidden.device)
+    ext().add_layernorm(hidden, delta, weight, out, rows, float(eps), status)
+    _launched()
+    return out
+
+
+class Mirrored:
+    """What a block leaves behind when nothing is pending: ``hidden`` holds every sum, and ``copy`` is the same
+    stream in the compute dtype (``hidden`` itself when that is float32), ready to be a product's operand."""
+
+    def __init__(self, hidden: torch.Tensor, copy: torch.Tensor):
+        self.hidden, self.copy = hidden, copy
+
+
+def branch_layernorm(hidden: torch.Tensor, branch: torch.Tensor, weight: torch.Tensor, eps: float,
+                     out_dtype: torch.dtype) -> torch.Tensor:
+    """``hidden += (branch - mean) / sqrt(var + eps) * weight`` in place, row by row in float32 (``branch`` in the
+    compute dtype or float32).  Returns the new ``hidden`` in ``out_dtype``: a rounded copy, or ``hidden`` itself
+    when ``out_dtype`` is float32."""
+    copy = None if out_dtype == torch.float32 else torch.empty(hidden.shape, dtype=out_dtype, device=hidden.device)
+    ext().branch_layernorm(hidden, branch, weight, copy, float(eps))
+    _launched()
+    return hidden if copy is None else copy
+
+
+def stream_copy(hidden: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The float32 stream as a product's operand: itself, or its rounding to ``dtype``."""
+    if dtype == torch.float32:
+        return hidden
+    out = torch.empty(hidden.shape, dtype=dtype, device=hidden.device)
+    ext().stream_copy(hidden, out)
+    _launched()
+    return out
+
+
+GLU_KINDS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+
+
+def glu(gate_up: torch.Tensor, kind: str, block: int = 0, limit: float = 0.0, slope: float = 1.0) -> torch.Tensor:
+    """``act(gate) * up`` of [tokens, 2 * intermediate]; gate and up columns alternate in runs of ``block`` columns
+    (0: all gate columns first).  ``kind``: ``"silu"``, ``"gelu_tanh"``, or ``"clamped_swish"``:
+    ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``, ``g * sigmoid(slope * g) * (u + 1)``."""
+    out = torch.empty((gate_up.shape[0], gate_up.shape[1] // 2), dtype=gate_up.dtype, device=gate_up.device)
+    ext().glu(gate_up, out, GLU_KINDS[kind], int(block), float(limit), float(slope))
     _launched()
     return out
 
@@ -305,16 +373,23 @@ def scored_attention(q, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq,
 
 
 def head_prep(x, slots, k_cache, v_cache, *, num_heads, num_kv_heads, head_dim, v_dim, unit_norm, eps, gated,
-              v_keep=None, v_other=None, blend_weight=None, status=None):
+              v_keep=None, v_other=None, blend_weight=None, q_weight=None, k_weight=None, has_kv=True, status=None):
     """From one product ``x`` [tokens, q heads | k heads | v heads | a gate column per q head]: q (and k) heads
-    scaled to unit RMS, ``v <- (1 - blend_weight) v + blend_weight v_other``, k and v written to their cache slots;
-    ``v_keep`` receives the layer's own values before the blend.  Returns (q [tokens, heads * head_dim], sigmoid of
+    scaled to unit RMS and multiplied by ``q_weight`` / ``k_weight`` (float32 [head_dim]) where given,
+    ``v <- (1 - blend_weight) v + blend_weight v_other``, k and v written to their cache slots;
+    ``v_keep`` receives the layer's own values before the blend.  Without ``has_kv`` the product holds no k and v
+    columns.  Returns (q [tokens, heads * head_dim], sigmoid of
     the gate columns as float32 [tokens, heads], or None without ``gated``)."""
     n = x.shape[0]
     q_out = torch.empty((n, num_heads * head_dim), dtype=x.dtype, device=x.device)
     gate = torch.empty((n, num_heads), dtype=torch.float32, device=x.device) if gated else None
-    ext().head_prep(x, slots, q_out, k_cache, v_cache, v_keep, v_other, blend_weight, gate, num_heads, num_kv_heads,
-                    head_dim, v_dim, bool(unit_norm), float(eps), status)
+    if q_weight is None and k_weight is None and has_kv:
+        ext().head_prep(x, slots, q_out, k_cache, v_cache, v_keep, v_other, blend_weight, gate, num_heads,
+                        num_kv_heads, head_dim, v_dim, bool(unit_norm), float(eps), status)
+    else:
+        ext().head_prep(x, slots, q_out, k_cache, v_cache, v_keep, v_other, blend_weight, gate, num_heads,
+                        num_kv_heads, head_dim, v_dim, bool(unit_norm), float(eps), status, q_weight, k_weight,
+                        bool(has_kv))
     _launched()
     return q_out, gate
 
@@ -355,6 +430,124 @@ def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
     """``relu(x) ** 2`` (``"relu2"``), the tanh form of GELU (``"gelu_tanh"``) or SiLU, element by element."""
     out = torch.empty_like(x)
     ext().activation(x, out, ACTIVATIONS[kind])
+    _launched()
+    return out
+
+
+# ----------------------------------------------------------------------------- the gated delta rule
+
+#: what the delta-rule kernels take: q/k width, value width (a block holds a value column per thread group), taps
+DELTA_MAX_DIM = 256
+DELTA_MAX_VDIM = 256
+DELTA_MAX_TAPS = 8
+
+
+def delta_shape(head_dim: int, v_dim: int) -> tuple[int, int] | None:
+    """(elements of a value column per lane, lanes per column) of the scan kernel for a head of these sizes, or None
+    when no form of it holds such a head (a block keeps a head's whole memory in registers: at most 1,024 threads of
+    up to 32 elements, 512 of 64 or 256 of 128)."""
+    if not (0 < head_dim <= DELTA_MAX_DIM and 0 < v_dim <= DELTA_MAX_VDIM):
+        return None
+    for per_lane in (8, 16, 32, 64, 128):
+        lanes = 1
+        while lanes * per_lane < head_dim:
+            lanes *= 2
+        limit = 1024 if per_lane <= 32 else (512 if per_lane <= 64 else 256)
+        if lanes <= 32 and (v_dim * lanes + 31) // 32 * 32 <= limit:
+            return per_lane, lanes
+    return None
+
+
+def delta_prep(x, conv, rate_log, step_bias, state, cu_q, state_slots, *, num_heads, num_kv_heads, head_dim, v_dim,
+               taps, unit_eps):
+    """From one product ``x`` [tokens, q | k | v | gate | beta | step] (``num_kv_heads`` heads of ``head_dim`` for q
+    and k, ``num_heads`` of ``v_dim`` for v and gate, a column per head for beta and step): q, k and v through their
+    causal convolutions over the sequence's own earlier tokens (``conv`` float32 [channels, taps], last tap the
+    current token's; before the step's first token the inputs come from ``state[slot, memory:]``, zeros at a
+    sequence's start) and SiLU; q and k scaled to unit length (q also by ``head_dim ** -0.5``);
+    ``beta = sigmoid(.)``, ``decay = exp(-exp(rate_log) * softplus(step + step_bias))``.  ``cu_q`` [sequences + 1]
+    gives each sequence's rows, ``state_slots`` its slot (negative: a padded sequence, left alone).  Returns
+    (float32 [tokens, q | k | v], float32 [tokens, beta per head | decay per head]).  The state is not changed."""
+    n = x.shape[0]
+    channels = 2 * num_kv_heads * head_dim + num_heads * v_dim
+    qkv = torch.empty((n, channels), dtype=torch.float32, device=x.device)
+    coef = torch.empty((n, 2 * num_heads), dtype=torch.float32, device=x.device)
+    ext().delta_prep(x, conv, rate_log, step_bias, state, cu_q, state_slots, qkv, coef, num_heads, num_kv_heads,
+                     head_dim, v_dim, taps, float(unit_eps))
+    _launched()
+    return qkv, coef
+
+
+def delta_scan(qkv, coef, x, norm_weight, state, cu_q, state_slots, *, num_heads, num_kv_heads, head_dim, v_dim, taps,
+               norm_eps):
+    """The recurrence over the step's tokens, sequence by sequence and head by head, from and into ``state``
+    [slots, heads * head_dim * v_dim + (taps - 1) * channels] float32: ``S *= decay; u = beta (v - S^T k);
+    S += k u^T; o = S^T q``; then ``o / sqrt(mean(o^2) + norm_eps) * norm_weight * silu(gate)`` with the gate columns
+    of ``x``.  Also moves the sequence's last ``taps - 1`` convolution inputs (columns of ``x``) into the state.
+    Returns [tokens, heads * v_dim] in the dtype of ``x``."""
+    out = torch.empty((x.shape[0], num_heads * v_dim), dtype=x.dtype, device=x.device)
+    scratch = torch.empty((x.shape[0], num_heads * v_dim), dtype=torch.float32, device=x.device)
+    ext().delta_scan(qkv, coef, x, norm_weight, state, cu_q, state_slots, scratch, out, num_heads, num_kv_heads,
+                     head_dim, v_dim, taps, float(norm_eps))
+    _launched()
+    return out
+
+
+# ----------------------------------------------------------------------------- routed experts
+
+MOE_MAX_EXPERTS = 512
+MOE_MAX_TOP = 16
+
+
+def moe_route(logits, correction, *, top, groups, keep_groups, group_top, scale, weight_eps):
+    """Scores ``sigmoid(logits)`` (float32 [tokens, experts]); choice scores are the scores plus ``correction``
+    (float32 [experts] or None); experts form ``groups`` equal runs, a group's score is the sum of its ``group_top``
+    largest choice scores, experts outside the ``keep_groups`` best groups cannot be chosen; the ``top`` largest
+    remaining choice scores are chosen (ties: the lower index).  Returns (int32 [tokens, top], float32 [tokens, top]:
+    the chosen scores divided by their sum plus ``weight_eps``, times ``scale``)."""
+    n = logits.shape[0]
+    chosen = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    ext().moe_route(logits, correction, chosen, weights, groups, keep_groups, group_top, float(scale), float(weight_eps))
+    _launched()
+    return chosen, weights
+
+
+def moe_sort(chosen, experts: int):
+    """The (token, choice) pairs in the order of their expert: ``order`` int32 [tokens * top] holds
+    ``token * top + choice``, ``offsets`` int32 [experts + 1] where each expert's run begins."""
+    order = torch.empty((chosen.numel(),), dtype=torch.int32, device=chosen.device)
+    offsets = torch.empty((experts + 1,), dtype=torch.int32, device=chosen.device)
+    ext().moe_sort(chosen, order, offsets)
+    _launched()
+    return order, offsets
+
+
+def moe_gate_up(x, w_gate_up, order, offsets, *, top, limit, slope):
+    """Row r of the result belongs to pair ``order[r]`` and is its expert's ``g * sigmoid(slope * g) * (u + 1)`` with
+    ``g = min(W_gate x, limit)``, ``u = clamp(W_up x, -limit, limit)`` for the pair's token;
+    ``w_gate_up`` [experts, gate rows then up rows, hidden].  [tokens * top, intermediate] in the dtype of ``x``."""
+    inter = w_gate_up.shape[1] // 2
+    act = torch.empty((order.numel(), inter), dtype=x.dtype, device=x.device)
+    ext().moe_gate_up(x, w_gate_up, order, offsets, act, top, float(limit), float(slope))
+    _launched()
+    return act
+
+
+def moe_down(act, w_down, order, offsets, weights):
+    """``weights[pair] * W_down[expert] act[r]`` for every sorted row r, written to row ``order[r]`` of a float32
+    [tokens * top, hidden]."""
+    out = torch.empty((order.numel(), w_down.shape[1]), dtype=torch.float32, device=act.device)
+    ext().moe_down(act, w_down, order, offsets, weights, out)
+    _launched()
+    return out
+
+
+def moe_combine(parts, shared, *, top):
+    """``sum over a token's choices of parts[token * top + choice] (+ shared[token])`` in that order, float32
+    [tokens, hidden]."""
+    out = torch.empty((parts.shape[0] // top, parts.shape[1]), dtype=torch.float32, device=parts.device)
+    ext().moe_combine(parts, shared, out, top)
     _launched()
     return out
 

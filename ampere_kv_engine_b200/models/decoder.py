@@ -13,8 +13,8 @@ import torch
 
 from ..config.spec import ModelSpec
 from ..kernels import ops
-from ..parts import (attention, block, embedding, feed_forward, latent_attention, norm, position,  # noqa: F401
-                     scored_attention)                          # (importing them registers the built-in kinds)
+from ..parts import (attention, block, embedding, feed_forward, gated_delta, latent_attention,  # noqa: F401
+                     norm, position, routed_experts, scored_attention)                          # (importing them registers the built-in kinds)
 from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, Block, CacheSpec, ParamSpec, build_part
 
 

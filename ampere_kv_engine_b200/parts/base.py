@@ -251,6 +251,8 @@ class Block:
                     return lazy
             delta.launch()
             return norm.forward(hidden, None, ctx, rows=rows)
+        if isinstance(delta, ops.Mirrored):
+            delta = None            # the stream holds everything; the copy is of no use to a norm
         if isinstance(delta, ops.Summed):
             if not norm.takes_summed:
                 return norm.forward(hidden, None, ctx, rows=rows)

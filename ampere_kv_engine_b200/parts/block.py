@@ -9,6 +9,7 @@ last product may add to the stream itself and the next product apply the norm (`
 
 from __future__ import annotations
 
+from ..kernels import ops
 from .base import Block, register_block
 
 
@@ -33,3 +34,39 @@ class PreNormBlock(Block):
             return hidden, attn
         x = self.run_norm(self.feed_forward_norm, hidden, attn, ctx, consumer=self.feed_forward)
         return hidden, self.run_branch(self.feed_forward, hidden, x, ctx)
+
+
+@register_block("postnorm")
+class PostNormBlock(Block):
+    """``h += norm1(mixer(h)); h += norm2(feed_forward(h))``: the branches read the stream itself and each norm sits
+    on its branch's output.  roles as ``prenorm``; the norms must offer ``add_normed``.  The stream is float32; in
+    bfloat16 every ``add_normed`` also leaves the stream's rounded copy, which the next branch reads and which
+    travels to the next block as an ``ops.Mirrored`` in place of a pending delta."""
+
+    def __init__(self, layer, **kw):
+        super().__init__(layer, **kw)
+        self.mixer = self.build_role("mixer")
+        self.mixer_norm = self.build_role("mixer_norm")
+        self.feed_forward = self.feed_forward_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward = self.build_role("feed_forward")
+            self.feed_forward_norm = self.build_role("feed_forward_norm")
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise ValueError(f"block kind 'postnorm': norm kind {norm.spec.kind!r} cannot norm a branch's output")
+
+    def forward(self, hidden, delta, ctx, cache):
+        if isinstance(delta, ops.Mirrored) and delta.hidden is hidden:
+            x = delta.copy
+        else:
+            if isinstance(delta, ops.PendingPhases):
+                delta.launch()
+                delta = None
+            if delta is not None and not isinstance(delta, (ops.Summed, ops.Mirrored)):
+                raise ValueError("block kind 'postnorm' follows a block that leaves its last branch unadded; "
+                                 "put a norm that adds it between them")
+            x = ops.stream_copy(hidden, self.dtype)
+        x = self.mixer_norm.add_normed(hidden, self.mixer.forward(x, ctx, cache), ctx)
+        if self.feed_forward is not None:
+            x = self.feed_forward_norm.add_normed(hidden, self.feed_forward.forward(x, ctx), ctx)
+        return hidden, ops.Mirrored(hidden, x)

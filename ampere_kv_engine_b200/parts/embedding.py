@@ -15,7 +15,9 @@ from .base import NORMS, Embedding, Head, ParamSpec, build_part, register_embedd
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Embedding):
-    """params: ``vocab_size``, ``tensor`` (the matrix's name under the prefix, default ``weight``)."""
+    """params: ``vocab_size``, ``tensor`` (the matrix's name under the prefix, default ``weight``), ``scale`` (the
+    row is multiplied by it, default 1), ``position_tensor`` and ``max_positions`` (a learned table
+    [max_positions, hidden] whose row of the token's position is added, unscaled; default none)."""
 
     graph_safe = True
 
@@ -24,17 +26,30 @@ class TokenEmbedding(Embedding):
         super().__init__(spec, **kw)
         self.vocab_size = int(spec.params["vocab_size"])
         self.tensor = str(spec.params.get("tensor", "weight"))
+        self.scale = float(spec.params.get("scale", 1.0))
+        self.position_tensor = spec.params.get("position_tensor")
+        self.max_positions = int(spec.params.get("max_positions") or 0)
+        if self.position_tensor is not None and self.max_positions <= 0:
+            raise ValueError("token_embedding: a position table needs 'max_positions'")
         self.weight: torch.Tensor | None = None
+        self.position_rows: torch.Tensor | None = None
 
     def param_specs(self):
-        return {self.tensor: ParamSpec((self.vocab_size, self.hidden_size))}
+        specs = {self.tensor: ParamSpec((self.vocab_size, self.hidden_size))}
+        if self.position_tensor is not None:
+            specs[str(self.position_tensor)] = ParamSpec((self.max_positions, self.hidden_size))
+        return specs
 
     def load(self, tensors):
         self.weight = tensors[self.tensor].contiguous()
+        if self.position_tensor is not None:
+            self.position_rows = tensors[str(self.position_tensor)].contiguous()
 
     def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
         return ops.embedding(token_ids, self.weight, status=getattr(ctx, "status", None),
-                             sampled=getattr(ctx, "sampled", None))
+                             sampled=getattr(ctx, "sampled", None), scale=self.scale,
+                             positions=ctx.positions if self.position_rows is not None else None,
+                             position_rows=self.position_rows)
 
 
 @register_embedding("normed_token_embedding")
@@ -59,7 +74,8 @@ class NormedTokenEmbedding(TokenEmbedding):
 @register_head("linear_head")
 class LinearHead(Head):
     """params: ``vocab_size``, ``tied`` (read the embedding's matrix instead of one's own), ``tensor`` (the
-    matrix's name under the prefix, default ``weight``).  A tied checkpoint may
+    matrix's name under the prefix, default ``weight``), ``softcap`` (the logits become ``cap * tanh(logits / cap)``;
+    default none).  A tied checkpoint may
     still carry the head's tensor: it is accepted if it equals the embedding's and refused if it differs."""
 
     graph_safe = True
@@ -70,6 +86,9 @@ class LinearHead(Head):
         self.vocab_size = int(spec.params["vocab_size"])
         self.tied = bool(spec.params.get("tied", False))
         self.tensor = str(spec.params.get("tensor", "weight"))
+        self.softcap = float(spec.params["softcap"]) if spec.params.get("softcap") else 0.0
+        if self.softcap < 0:
+            raise ValueError("linear_head: softcap must be positive")
         self.weight: torch.Tensor | None = None
 
     def param_specs(self):
@@ -97,4 +116,5 @@ class LinearHead(Head):
         self.weight = embedding.weight
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, out_dtype=torch.float32)
+        logits = ops.linear(x, self.weight, out_dtype=torch.float32)
+        return ops.softcap_(logits, self.softcap) if self.softcap else logits

@@ -52,3 +52,36 @@ class RMSNorm(Norm):
                 return ops.LazyNorm(delta, self.weight, self.eps, self.dtype, status)
             delta = None      # hidden holds the sum already
         return ops.add_rmsnorm(hidden, delta, self.weight, self.eps, self.dtype, rows=rows, status=status)
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * weight`` with the variance as the mean of squared deviations and no bias.
+    params: ``size`` (defaults to the hidden size), ``eps``, ``tensor`` (the weight's name under the prefix, default
+    ``weight``).  Beside the usual form (:meth:`forward`: sum into the stream, then norm what a branch reads) it has
+    the form a layer with normed branch *outputs* needs (:meth:`add_normed`): the norm of the branch's result is what
+    is added to the stream.  Mean, variance, the scale and the sum are float32."""
+
+    graph_safe = True
+
+    def __init__(self, spec, **kw):
+        super().__init__(spec, **kw)
+        self.size = int(spec.params.get("size", self.hidden_size))
+        self.eps = float(spec.params["eps"])
+        self.tensor = str(spec.params.get("tensor", "weight"))
+        self.weight: torch.Tensor | None = None
+
+    def param_specs(self):
+        return {self.tensor: ParamSpec((self.size,), kind="vector", init="norm")}
+
+    def load(self, tensors):
+        self.weight = tensors[self.tensor].contiguous()
+
+    def forward(self, hidden, delta, ctx, rows=None):
+        return ops.add_layernorm(hidden, delta, self.weight, self.eps, self.dtype, rows=rows,
+                                 status=getattr(ctx, "status", None))
+
+    def add_normed(self, hidden, branch, ctx):
+        """``hidden += LN(branch)`` in place; returns the new stream in the compute dtype (the stream itself when
+        that is float32), which is what the next branch reads."""
+        return ops.branch_layernorm(hidden, branch, self.weight, self.eps, self.dtype)

@@ -3,12 +3,17 @@ different widths.
 
     q, k, v, g = (W_q | W_k | W_v | W_g) x            one product; g: one column per q head (optional)
     q, k       <- each head divided by sqrt(mean(head^2) + eps)          (``unit_norm``)
+    q, k       <- times a learned weight per dim, shared by the heads    (``norm_weights``)
     v          <- (1 - lam) v + lam v_first             (``value_blend`` "reader"; a "source" layer publishes its v)
     s(i, j)    = q_i . k_j * scale
     s          <- cap * tanh(s / cap)                   (``softcap``)
     s          <- s - slope_h (i - j),  slope_h = 2 ** (-slope_span (h + 1) / heads)       (``slope_span``)
     i sees j   iff j <= i and both lie in the same block of ``chunk`` positions counted from the sequence's start
     out_h      = softmax(s) v * sigmoid(g_h);   y = W_o out
+
+A mixer without ``own_kv`` has no key and value projections: it reads the pages an earlier schedule position wrote
+(the model's schedule names it), with its own queries.  When nothing is done to the scores, keys and values have one
+width and the plain attention kernels take that width, those run.
 
 Positions enter through the distance bias and the blocks only.  Keys (after the norm) and values (after the blend)
 are what the pages keep; a block's pages are given back once the sequence has moved past it.  Everything between
@@ -26,7 +31,8 @@ from .base import CacheSpec, CacheTensor, Mixer, ParamSpec, register_mixer
 @register_mixer("scored_attention")
 class ScoredAttention(Mixer):
     """params: ``num_heads``, ``num_kv_heads``, ``head_dim`` (query / key width), ``v_dim`` (value width),
-    ``scale``, ``unit_norm`` (bool) and ``norm_eps``, ``softcap`` (None: none), ``slope_span`` (None: no distance
+    ``scale``, ``unit_norm`` (bool) and ``norm_eps``, ``norm_weights`` (bool: the unit-RMS q and k heads are multiplied
+    by learned weights ``q_norm`` / ``k_norm``), ``own_kv`` (bool, default True), ``softcap`` (None: none), ``slope_span`` (None: no distance
     bias), ``chunk`` (None: plain causal), ``window`` (None: all keys of the block), ``gated`` (bool),
     ``value_blend`` (None, ``"source"`` or ``"reader"``) and ``blend_key`` (the name under which the source's values
     travel through the step), ``names`` (local tensor names of q, k, v, gate, out, blend)."""
@@ -36,7 +42,7 @@ class ScoredAttention(Mixer):
     adds_residual = True
 
     NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "gate": "gate_proj.weight",
-             "out": "o_proj.weight", "blend": "value_blend"}
+             "out": "o_proj.weight", "blend": "value_blend", "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
 
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)
@@ -51,6 +57,10 @@ class ScoredAttention(Mixer):
         self.scale = float(p["scale"]) if p.get("scale") is not None else self.head_dim ** -0.5
         self.unit_norm = bool(p.get("unit_norm", False))
         self.norm_eps = float(p.get("norm_eps", 1e-6))
+        self.norm_weights = bool(p.get("norm_weights", False))
+        self.own_kv = bool(p.get("own_kv", True))
+        if self.norm_weights and not self.unit_norm:
+            raise ValueError("scored_attention: norm_weights go with unit_norm")
         self.softcap = float(p["softcap"]) if p.get("softcap") else 0.0
         self.slope_span = float(p["slope_span"]) if p.get("slope_span") is not None else None
         self.chunk = int(p["chunk"]) if p.get("chunk") else 0
@@ -61,16 +71,21 @@ class ScoredAttention(Mixer):
         self.value_blend = p.get("value_blend")
         if self.value_blend not in (None, "source", "reader"):
             raise ValueError(f"scored_attention: value_blend must be None, 'source' or 'reader', got {self.value_blend!r}")
+        if self.value_blend is not None and not self.own_kv:
+            raise ValueError("scored_attention: a mixer without keys and values of its own has no values to blend")
         self.blend_key = str(p.get("blend_key", "value_blend"))
         self.names = dict(self.NAMES, **(p.get("names") or {}))
         self.slopes = None
         if self.slope_span is not None:
             h = torch.arange(1, self.num_heads + 1, dtype=torch.float64)
             self.slopes = torch.exp2(-self.slope_span * h / self.num_heads).to(torch.float32).to(self.device)
-        self.w_in = self.w_o = self.blend_weight = None
+        self.w_in = self.w_o = self.blend_weight = self.q_norm_weight = self.k_norm_weight = None
+        #: nothing is done to the scores and keys and values have one width that the plain kernels take
+        self.plain_scores = (not self.softcap and self.slope_span is None and not self.chunk and not self.gated
+                             and self.head_dim == self.v_dim and self.head_dim % 16 == 0 and self.head_dim <= 256)
 
     def preferred_q_tile(self):
-        if self.head_dim == self.v_dim == 128:
+        if self.head_dim == self.v_dim == 128 or self.plain_scores:
             return ops.attention_q_tile(self.head_dim, self.num_heads // self.num_kv_heads)
         return None
 
@@ -83,11 +98,14 @@ class ScoredAttention(Mixer):
 
     def param_specs(self):
         h, n = self.hidden_size, self.names
-        specs = {
-            n["q"]: ParamSpec((self.num_heads * self.head_dim, h)),
-            n["k"]: ParamSpec((self.num_kv_heads * self.head_dim, h)),
-            n["v"]: ParamSpec((self.num_kv_heads * self.v_dim, h)),
-        }
+        specs = {n["q"]: ParamSpec((self.num_heads * self.head_dim, h))}
+        if self.own_kv:
+            specs[n["k"]] = ParamSpec((self.num_kv_heads * self.head_dim, h))
+            specs[n["v"]] = ParamSpec((self.num_kv_heads * self.v_dim, h))
+        if self.norm_weights:
+            specs[n["q_norm"]] = ParamSpec((self.head_dim,), kind="vector", init="norm")
+            if self.own_kv:
+                specs[n["k_norm"]] = ParamSpec((self.head_dim,), kind="vector", init="norm")
         # a source layer carries the scalar too and does not use it; a layer that does not blend may carry it
         specs[n["blend"]] = ParamSpec((), kind="vector", init="unit_interval", optional=self.value_blend is None)
         if self.gated:
@@ -97,8 +115,12 @@ class ScoredAttention(Mixer):
 
     def load(self, tensors):
         n = self.names
-        rows = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]] + ([tensors[n["gate"]]] if self.gated else [])
+        rows = [tensors[n["q"]]] + ([tensors[n["k"]], tensors[n["v"]]] if self.own_kv else []) \
+            + ([tensors[n["gate"]]] if self.gated else [])
         self.w_in = torch.cat(rows, dim=0).contiguous()
+        if self.norm_weights:
+            self.q_norm_weight = tensors[n["q_norm"]].contiguous()
+            self.k_norm_weight = tensors[n["k_norm"]].contiguous() if self.own_kv else None
         self.w_o = tensors[n["out"]].contiguous()
         if self.value_blend == "reader":
             self.blend_weight = tensors[n["blend"]].reshape(1).contiguous()
@@ -117,16 +139,20 @@ class ScoredAttention(Mixer):
             if v_other is None or v_other.shape != (tokens, self.num_kv_heads * self.v_dim):
                 raise ValueError(f"scored_attention: no layer before this one left values of "
                                  f"[{tokens}, {self.num_kv_heads * self.v_dim}] under {self.blend_key!r}")
-        writes = cache.writes
+        writes = cache.writes and self.own_kv
+        if cache.writes != self.own_kv:
+            raise ValueError("scored_attention: a mixer with keys and values of its own writes its pages, one without "
+                             "reads another position's (the schedule's cache_of)")
         q, gate = ops.head_prep(
             x, group.slot_mapping if writes else None, k_cache if writes else None, v_cache if writes else None,
             num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, v_dim=self.v_dim,
             unit_norm=self.unit_norm, eps=self.norm_eps, gated=self.gated, v_keep=v_keep, v_other=v_other,
-            blend_weight=self.blend_weight, status=ctx.status)
+            blend_weight=self.blend_weight, q_weight=self.q_norm_weight, k_weight=self.k_norm_weight,
+            has_kv=self.own_kv, status=ctx.status)
         out = torch.empty((tokens, self.num_heads * self.v_dim), dtype=q.dtype, device=q.device)
         run_attention(ctx, group, q, k_cache, v_cache, out, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
                       v_dim=self.v_dim, scale=self.scale, window=self.window, chunk=self.chunk, softcap=self.softcap,
-                      slopes=self.slopes, gate=gate)
+                      slopes=self.slopes, gate=gate, plain=self.plain_scores)
         if residual is not None:
             summed = ops.linear_into_residual(out, self.w_o, residual, status=ctx.status)
             if summed is not None:
@@ -135,10 +161,13 @@ class ScoredAttention(Mixer):
 
 
 def run_attention(ctx, group, q, k_cache, v_cache, out, *, num_heads, num_kv_heads, v_dim, scale, window=0, chunk=0,
-                  softcap=0.0, slopes=None, gate=None) -> None:
+                  softcap=0.0, slopes=None, gate=None, plain=False) -> None:
     """``ops.scored_attention`` over the step's tiles: the single-token tiles of a mixed step (they come first) apart
-    from the prompt tiles, each with the number of key splits that fills the GPU."""
+    from the prompt tiles, each with the number of key splits that fills the GPU.  ``plain``: nothing is done to the
+    scores and the plain kernels take the sizes: ``ops.paged_attention`` runs instead."""
     group_size = num_heads // num_kv_heads
+    plain_tc = plain and ops.attention_takes_tensor_cores(q.dtype, q.shape[1] // num_heads, group_size,
+                                                          k_cache.shape[2])
     first = getattr(ctx, "num_decode_tiles", 0)
     for lo, hi, q_tile in ((0, first, 1), (first, ctx.num_tiles, ctx.q_tile)):
         if hi <= lo:
@@ -147,6 +176,14 @@ def run_attention(ctx, group, q, k_cache, v_cache, out, *, num_heads, num_kv_hea
         for limit in (window, chunk):
             if limit:
                 longest, mean = min(longest, limit), min(mean, limit)
+        if plain:
+            splits = 1 if q_tile > 1 and plain_tc else ops.choose_splits(
+                hi - lo, num_kv_heads, q_tile * group_size, longest, plain_tc, mean_context=mean)
+            ops.paged_attention(
+                q, k_cache, v_cache, group.block_table, ctx.cu_q, ctx.ctx_lens, ctx.tile_seq[lo:hi], ctx.tile_q0[lo:hi],
+                ctx.tile_nq[lo:hi], num_tiles=hi - lo, q_tile=q_tile, num_splits=splits, num_heads=num_heads,
+                num_kv_heads=num_kv_heads, window=window, scale=scale, status=ctx.status, out=out)
+            continue
         tensor_core = k_cache is not v_cache and ops.scored_takes_tensor_cores(
             q.dtype, q.shape[1] // num_heads, v_dim, group_size, k_cache.shape[2], prompt=q_tile > 1)
         if k_cache is v_cache and ops.shared_rows_take_tensor_cores(q.dtype, q.shape[1] // num_heads, v_dim):

@@ -18,11 +18,56 @@ class FakeExt:
     def smoke_add(self, a, b):
         return a + b
 
-    def embedding(self, ids, table, hidden, status=None, sampled=None):
+    def embedding(self, ids, table, hidden, status=None, sampled=None, scale=1.0, positions=None, position_rows=None):
         ids = ids.long()
         if sampled is not None:
             ids = torch.where(ids < 0, sampled.long()[(-ids - 1).clamp(min=0)], ids)
-        hidden.copy_(table[ids].float())
+        rows = table[ids].float() * scale
+        if position_rows is not None:
+            rows = rows + position_rows[positions.long()].float()
+        hidden.copy_(rows)
+
+    def softcap(self, logits, cap):
+        logits.copy_(cap * torch.tanh(logits / cap))
+
+    @staticmethod
+    def _layer_norm(x, weight, eps):
+        mu = x.mean(-1, keepdim=True)
+        var = (x - mu).square().mean(-1, keepdim=True)
+        return (x - mu) * torch.rsqrt(var + eps) * weight
+
+    def add_layernorm(self, hidden, delta, weight, out, rows, eps, status=None):
+        if rows is None:
+            if delta is not None:
+                hidden += delta.float()
+            x = hidden
+        else:
+            x = hidden[rows.long()]
+            if delta is not None:
+                x = x + delta[rows.long()].float()
+        out.copy_(self._layer_norm(x, weight, eps).to(out.dtype))
+
+    def branch_layernorm(self, hidden, branch, weight, copy, eps):
+        hidden += self._layer_norm(branch.float(), weight, eps)
+        if copy is not None:
+            copy.copy_(hidden.to(copy.dtype))
+
+    def stream_copy(self, hidden, out):
+        out.copy_(hidden.to(out.dtype))
+
+    def glu(self, gate_up, out, kind, block, limit, slope):
+        inter = gate_up.shape[1] // 2
+        block = block or inter
+        pairs = gate_up.float().view(gate_up.shape[0], inter // block, 2, block)
+        g, u = pairs[:, :, 0].reshape(-1, inter), pairs[:, :, 1].reshape(-1, inter)
+        if kind == 0:
+            y = g * torch.sigmoid(g) * u
+        elif kind == 1:
+            y = 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3))) * u
+        else:
+            g, u = g.clamp(max=limit), u.clamp(min=-limit, max=limit)
+            y = g * torch.sigmoid(slope * g) * (u + 1)
+        out.copy_(y.to(out.dtype))
 
     def add_rmsnorm(self, hidden, delta, weight, out, rows, eps, status=None):
         if delta is not None and delta.dim() == 3:
@@ -176,15 +221,21 @@ class FakeExt:
             out[q0:q1] = o.reshape(n, -1).to(out.dtype)
 
     def head_prep(self, x, slots, q_out, k_cache, v_cache, v_keep, v_other, blend_weight, gate_out, num_heads,
-                  num_kv_heads, head_dim, v_dim, unit_norm, eps, status=None):
+                  num_kv_heads, head_dim, v_dim, unit_norm, eps, status=None, q_weight=None, k_weight=None,
+                  has_kv=True):
         n = x.shape[0]
         xf = x.float()
-        a, b, c = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * v_dim
-        q, k, v = xf[:, :a].view(n, num_heads, head_dim), xf[:, a:a + b].view(n, num_kv_heads, head_dim), \
-            xf[:, a + b:a + b + c].view(n, num_kv_heads, v_dim)
+        a = num_heads * head_dim
+        b, c = (num_kv_heads * head_dim, num_kv_heads * v_dim) if has_kv else (0, 0)
+        q, k, v = xf[:, :a].view(n, num_heads, head_dim), xf[:, a:a + b].view(n, -1, head_dim), \
+            xf[:, a + b:a + b + c].view(n, -1, v_dim)
         if unit_norm:
             q = q * torch.rsqrt(q.square().mean(-1, keepdim=True) + eps)
             k = k * torch.rsqrt(k.square().mean(-1, keepdim=True) + eps)
+        if q_weight is not None:
+            q = q * q_weight
+        if k_weight is not None:
+            k = k * k_weight
         q_out.copy_(q.reshape(n, -1).to(q_out.dtype))
         if v_keep is not None:
             v_keep.copy_(v.reshape(n, -1).to(v_keep.dtype))
@@ -242,3 +293,113 @@ class FakeExt:
         else:
             y = z / (1 + torch.exp(-z))
         out.copy_(y.to(out.dtype))
+
+    # ------------------------------------------------------------------ the gated delta rule
+
+    def delta_prep(self, x, conv, rate_log, step_bias, state, cu_q, state_slots, qkv, coef, num_heads, num_kv_heads,
+                   head_dim, v_dim, taps, unit_eps):
+        G, D, H, V = num_kv_heads, head_dim, num_heads, v_dim
+        channels = 2 * G * D + H * V
+        memory = H * D * V
+        cu, slots = cu_q.tolist(), state_slots.tolist()
+        xf = x.float()
+        qkv.zero_()
+        coef.zero_()
+        for s, slot in enumerate(slots):
+            q0, q1 = cu[s], cu[s + 1]
+            if slot < 0 or q1 <= q0:
+                continue
+            before = state[slot, memory:].view(taps - 1, channels)
+            stream = torch.cat((before, xf[q0:q1, :channels]), dim=0)
+            y = torch.zeros(q1 - q0, channels)
+            for j in range(taps):
+                y = y + stream[j:j + q1 - q0] * conv[:, j]
+            y = y * torch.sigmoid(y)
+            q, k = y[:, :G * D].view(-1, G, D), y[:, G * D:2 * G * D].view(-1, G, D)
+            q = q * torch.rsqrt(q.square().sum(-1, keepdim=True) + unit_eps) * D ** -0.5
+            k = k * torch.rsqrt(k.square().sum(-1, keepdim=True) + unit_eps)
+            qkv[q0:q1] = torch.cat((q.reshape(q1 - q0, -1), k.reshape(q1 - q0, -1), y[:, 2 * G * D:]), dim=1)
+            tail = xf[q0:q1, channels + H * V:]
+            coef[q0:q1, :H] = torch.sigmoid(tail[:, :H])
+            coef[q0:q1, H:] = torch.exp(-torch.exp(rate_log) * torch.nn.functional.softplus(tail[:, H:] + step_bias))
+
+    def delta_scan(self, qkv, coef, x, norm_weight, state, cu_q, state_slots, scratch, out, num_heads, num_kv_heads,
+                   head_dim, v_dim, taps, norm_eps):
+        G, D, H, V = num_kv_heads, head_dim, num_heads, v_dim
+        channels = 2 * G * D + H * V
+        memory = H * D * V
+        cu, slots = cu_q.tolist(), state_slots.tolist()
+        out.zero_()
+        for s, slot in enumerate(slots):
+            q0, q1 = cu[s], cu[s + 1]
+            if slot < 0 or q1 <= q0:
+                continue
+            S = state[slot, :memory].view(H, D, V).clone()
+            for t in range(q0, q1):
+                q, k = qkv[t, :G * D].view(G, D), qkv[t, G * D:2 * G * D].view(G, D)
+                v = qkv[t, 2 * G * D:].view(H, V)
+                gate = x[t, channels:channels + H * V].float().view(H, V)
+                for h in range(H):
+                    j = h // (H // G)
+                    S[h] = S[h] * coef[t, H + h]
+                    u = coef[t, h] * (v[h] - S[h].T @ k[j])
+                    S[h] = S[h] + torch.outer(k[j], u)
+                    o = S[h].T @ q[j]
+                    o = o * torch.rsqrt(o.square().mean() + norm_eps) * norm_weight * (gate[h] * torch.sigmoid(gate[h]))
+                    out[t, h * V:(h + 1) * V] = o.to(out.dtype)
+            state[slot, :memory] = S.reshape(-1)
+            if taps > 1:
+                before = state[slot, memory:].view(taps - 1, channels)
+                stream = torch.cat((before, x[q0:q1, :channels].float()), dim=0)
+                state[slot, memory:] = stream[-(taps - 1):].reshape(-1)
+
+    # ------------------------------------------------------------------ routed experts
+
+    def moe_route(self, logits, correction, chosen, weights, groups, keep_groups, group_top, scale, weight_eps):
+        n, E = logits.shape
+        top = chosen.shape[1]
+        s = torch.sigmoid(logits.float())
+        c = s if correction is None else s + correction
+        per = E // groups
+        grouped = c.view(n, groups, per)
+        score = grouped.topk(min(group_top, per), dim=-1).values.sum(-1)
+        # ties go to the lower index: a stable sort, descending
+        kept = torch.sort(score, dim=-1, descending=True, stable=True).indices[:, :keep_groups]
+        allowed = torch.zeros(n, groups, dtype=torch.bool).scatter_(1, kept, True)
+        masked = torch.where(allowed[:, :, None].expand(n, groups, per), grouped,
+                             torch.full_like(grouped, -math.inf)).reshape(n, E)
+        ids = torch.sort(masked, dim=-1, descending=True, stable=True).indices[:, :top]
+        picked = s.gather(1, ids)
+        chosen.copy_(ids.to(torch.int32))
+        weights.copy_(picked / (picked.sum(-1, keepdim=True) + weight_eps) * scale)
+
+    def moe_sort(self, chosen, order, offsets):
+        flat = chosen.reshape(-1).long()
+        order.copy_(torch.sort(flat, stable=True).indices.to(torch.int32))
+        counts = torch.bincount(flat, minlength=offsets.numel() - 1)
+        offsets[0] = 0
+        offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
+
+    def moe_gate_up(self, x, w_gate_up, order, offsets, act, top, limit, slope):
+        inter = w_gate_up.shape[1] // 2
+        off = offsets.tolist()
+        for e in range(len(off) - 1):
+            rows = order[off[e]:off[e + 1]].long()
+            if rows.numel() == 0:
+                continue
+            both = x[rows // top].float() @ w_gate_up[e].float().T
+            g, u = both[:, :inter].clamp(max=limit), both[:, inter:].clamp(min=-limit, max=limit)
+            act[off[e]:off[e + 1]] = (g * torch.sigmoid(slope * g) * (u + 1)).to(act.dtype)
+
+    def moe_down(self, act, w_down, order, offsets, weights, out):
+        off = offsets.tolist()
+        flat = weights.reshape(-1)
+        for e in range(len(off) - 1):
+            rows = order[off[e]:off[e + 1]].long()
+            if rows.numel() == 0:
+                continue
+            out[rows] = (act[off[e]:off[e + 1]].float() @ w_down[e].float().T) * flat[rows][:, None]
+
+    def moe_combine(self, parts, shared, out, top):
+        total = parts.view(-1, top, parts.shape[1]).sum(1)
+        out.copy_(total if shared is None else total + shared.float())
