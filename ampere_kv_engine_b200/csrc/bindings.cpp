@@ -1177,7 +1177,7 @@ void moe_sort(const Tensor& chosen, Tensor& order, Tensor& offsets) {
 }
 
 void moe_gate_up(const Tensor& x, const Tensor& w, const Tensor& order, const Tensor& offsets, Tensor& act, int64_t top,
-                 double limit, double slope) {
+                 double limit, double slope, bool plain) {
   check_cuda(x, "x");
   check_cuda(w, "w");
   check_cuda(act, "act");
@@ -1204,12 +1204,13 @@ void moe_gate_up(const Tensor& x, const Tensor& w, const Tensor& order, const Te
   p.limit = (float)limit;
   p.slope = (float)slope;
   p.dtype = dtype_code(x, "x");
+  p.force_plain = plain ? 1 : 0;
   c10::cuda::CUDAGuard guard(x.device());
   check_launch(akv::launch_moe_gemm(p, true, stream_of(x)), "moe_gate_up");
 }
 
 void moe_down(const Tensor& act, const Tensor& w, const Tensor& order, const Tensor& offsets, const Tensor& weights,
-              Tensor& out) {
+              Tensor& out, bool plain) {
   check_cuda(act, "act");
   check_cuda(w, "w");
   check_same(act, w, "act", "w");
@@ -1233,6 +1234,7 @@ void moe_down(const Tensor& act, const Tensor& w, const Tensor& order, const Ten
   p.n = (int)hidden;
   p.top = 1;
   p.dtype = dtype_code(act, "act");
+  p.force_plain = plain ? 1 : 0;
   c10::cuda::CUDAGuard guard(act.device());
   check_launch(akv::launch_moe_gemm(p, false, stream_of(act)), "moe_down");
 }
@@ -1360,9 +1362,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("groups"), py::arg("keep_groups"), py::arg("group_top"), py::arg("scale"), py::arg("weight_eps"));
   m.def("moe_sort", &moe_sort, py::arg("chosen"), py::arg("order"), py::arg("offsets"));
   m.def("moe_gate_up", &moe_gate_up, py::arg("x"), py::arg("w"), py::arg("order"), py::arg("offsets"), py::arg("act"),
-        py::arg("top"), py::arg("limit"), py::arg("slope"));
+        py::arg("top"), py::arg("limit"), py::arg("slope"), py::arg("plain") = false);
   m.def("moe_down", &moe_down, py::arg("act"), py::arg("w"), py::arg("order"), py::arg("offsets"), py::arg("weights"),
-        py::arg("out"));
+        py::arg("out"), py::arg("plain") = false);
   m.def("moe_combine", &moe_combine, py::arg("parts"), py::arg("shared"), py::arg("out"), py::arg("top"));
   m.def("paged_attention", &paged_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"),
         py::arg("block_table"), py::arg("cu_q"), py::arg("ctx_lens"), py::arg("tile_seq"), py::arg("tile_q0"),

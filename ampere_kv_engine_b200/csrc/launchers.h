@@ -350,6 +350,7 @@ struct MoeGemmParams {
   int experts, k, n, top;
   float limit, slope;
   int dtype;
+  int force_plain;             // 1: the float-arithmetic form even where the tensor-core form takes the sizes
 };
 int launch_moe_gemm(const MoeGemmParams& p, bool gated, cudaStream_t stream);
 // out[t] = sum over c < top of parts[t * top + c] (+ shared[t]), float32.

@@ -294,9 +294,208 @@ __global__ void __launch_bounds__(kGemmThreads) moe_gemm_kernel(MoeGemmParams p)
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// The same products on the tensor cores, for bfloat16 with k a multiple of eight (16-byte copies): 64 sorted rows of
+// one expert times 128 weight rows (gated: 64 gate rows and the 64 up rows of the same features), k in steps of 32
+// through a three-stage cp.async ring, ldmatrix + mma.sync m16n8k16 with float accumulators.  Eight warps, two along
+// the rows and four along the features; in the gated product a warp holds 16 gate features and the same 16 up
+// features, so the activation is applied to its own accumulators.
+namespace {
+constexpr int kMmaRows = 64, kMmaWeightRows = 128, kMmaK = 32, kMmaStages = 3, kMmaPitch = kMmaK + 8;
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* global, bool valid) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;                 // zero bytes read: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(global), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void find_tile_of(const int32_t* offsets, int experts, int tile, int tile_rows, int& expert,
+                                             int& row0, int& rows) {
+  rows = 0;
+  expert = row0 = 0;
+  int seen = 0;
+  for (int e = 0; e < experts; ++e) {
+    const int begin = offsets[e], count = offsets[e + 1] - begin;
+    const int tiles = (count + tile_rows - 1) / tile_rows;
+    if (tile < seen + tiles) {
+      expert = e;
+      row0 = begin + (tile - seen) * tile_rows;
+      rows = min(tile_rows, begin + count - row0);
+      return;
+    }
+    seen += tiles;
+  }
+}
+}  // namespace
+
+template <bool GATED>
+__global__ void __launch_bounds__(256) moe_gemm_mma_kernel(MoeGemmParams p) {
+  __shared__ __align__(16) __nv_bfloat16 a_smem[kMmaStages][kMmaRows][kMmaPitch];
+  __shared__ __align__(16) __nv_bfloat16 w_smem[kMmaStages][kMmaWeightRows][kMmaPitch];
+  __shared__ int tile_info[3];
+  __shared__ int64_t row_source[kMmaRows];
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    int e, r0, n;
+    find_tile_of(p.offsets, p.experts, blockIdx.y, kMmaRows, e, r0, n);
+    tile_info[0] = e;
+    tile_info[1] = r0;
+    tile_info[2] = n;
+  }
+  __syncthreads();
+  const int expert = tile_info[0], row0 = tile_info[1], rows = tile_info[2];
+  if (rows == 0) return;
+  const int K = p.k, N = p.n;
+  constexpr int kCols = GATED ? kMmaWeightRows / 2 : kMmaWeightRows;      // output features of the tile
+  const int col0 = blockIdx.x * kCols;
+  if (threadIdx.x < kMmaRows) {
+    const int r = threadIdx.x;
+    int64_t src = -1;
+    if (r < rows) src = GATED ? (int64_t)(p.order[row0 + r] / p.top) : (int64_t)(row0 + r);
+    row_source[r] = src;
+  }
+  __syncthreads();
+  const __nv_bfloat16* a = (const __nv_bfloat16*)p.a;
+  const __nv_bfloat16* w = (const __nv_bfloat16*)p.w + (int64_t)expert * (GATED ? 2 : 1) * N * K;
+
+  // this thread's copies of a stage: one 16-byte piece of the rows' tile, two of the weights' tile
+  const int a_row = threadIdx.x >> 2, piece = threadIdx.x & 3;
+  const int64_t a_src = row_source[a_row];
+  int64_t w_src[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int wr = (threadIdx.x >> 2) + 64 * i;               // row of the weights' tile
+    int64_t row;
+    if (GATED) row = wr < 64 ? (int64_t)col0 + wr : (int64_t)N + col0 + (wr - 64);
+    else row = (int64_t)col0 + wr;
+    const bool inside = GATED ? (col0 + (wr & 63) < N) : (col0 + wr < N);
+    w_src[i] = inside ? row : -1;
+  }
+  auto issue = [&](int stage, int k0) {
+    const int k = k0 + piece * 8;
+    const bool in_k = k < K;
+    cp_async_16(&a_smem[stage][a_row][piece * 8], a + (a_src >= 0 && in_k ? a_src * K + k : 0), a_src >= 0 && in_k);
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      cp_async_16(&w_smem[stage][(threadIdx.x >> 2) + 64 * i][piece * 8], w + (w_src[i] >= 0 && in_k ? w_src[i] * K + k : 0),
+                  w_src[i] >= 0 && in_k);
+  };
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int wm = warp >> 2, wn = warp & 3;                    // 2 x 4 warps
+  // the four 8-feature tiles of this warp, as rows of the weights' tile
+  int n_base[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    n_base[j] = GATED ? (j < 2 ? wn * 16 + j * 8 : 64 + wn * 16 + (j - 2) * 8) : wn * 32 + j * 8;
+  float acc[2][4][4] = {};
+  const int steps = (K + kMmaK - 1) / kMmaK;
+#pragma unroll
+  for (int s = 0; s < kMmaStages - 1; ++s) {
+    if (s < steps) issue(s, s * kMmaK);
+    cp_async_commit();
+  }
+  for (int step = 0; step < steps; ++step) {
+    cp_async_wait<kMmaStages - 2>();
+    __syncthreads();
+    const int next = step + kMmaStages - 1;
+    if (next < steps) issue(next % kMmaStages, next * kMmaK);
+    cp_async_commit();
+    const int stage = step % kMmaStages;
+#pragma unroll
+    for (int kk = 0; kk < kMmaK; kk += 16) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        ldmatrix_x4(af[i], &a_smem[stage][wm * 32 + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        // two 8-feature tiles at a time: lanes 0-15 address the first, 16-31 the second; within each, lanes 8-15 the
+        // upper half of k
+        uint32_t bf[4];
+        const int nb = (lane < 16) ? n_base[j] : n_base[j + 1];
+        ldmatrix_x4(bf, &w_smem[stage][nb + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          mma_bf16(acc[i][j], af[i], bf[0], bf[1]);
+          mma_bf16(acc[i][j + 1], af[i], bf[2], bf[3]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  // accumulator element e of tile (i, j): row wm * 32 + i * 16 + lane / 4 (+ 8 for e >= 2), feature (lane % 4) * 2 + (e & 1)
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = wm * 32 + i * 16 + (lane >> 2) + half * 8;
+      if (r >= rows) continue;
+      if (GATED) {
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (int64_t)(row0 + r) * N;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int c = col0 + wn * 16 + j * 8 + (lane & 3) * 2 + e;
+            if (c >= N) continue;
+            const float g = fminf(acc[i][j][half * 2 + e], p.limit);
+            const float u = fminf(fmaxf(acc[i][j + 2][half * 2 + e], -p.limit), p.limit);
+            dst[c] = __float2bfloat16_rn(g / (1.f + expf(-p.slope * g)) * (u + 1.f));
+          }
+        }
+      } else {
+        const int pair = p.order[row0 + r];
+        const float weight = p.weights[pair];
+        float* dst = (float*)p.out + (int64_t)pair * N;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int c = col0 + wn * 32 + j * 8 + (lane & 3) * 2 + e;
+            if (c < N) dst[c] = weight * acc[i][j][half * 2 + e];
+          }
+        }
+      }
+    }
+  }
+}
+
+static bool moe_gemm_takes_mma(const MoeGemmParams& p) {
+  return p.dtype == kBFloat16 && p.k % 8 == 0 &&
+         (reinterpret_cast<uintptr_t>(p.a) | reinterpret_cast<uintptr_t>(p.w)) % 16 == 0;
+}
+
 int launch_moe_gemm(const MoeGemmParams& p, bool gated, cudaStream_t stream) {
   if (p.pairs == 0) return 0;
   if (p.experts <= 0 || p.experts > kMoeMaxExperts || p.k <= 0 || p.n <= 0 || p.top <= 0) return (int)cudaErrorInvalidValue;
+  if (moe_gemm_takes_mma(p) && !p.force_plain) {
+    const int64_t row_tiles = p.pairs / kMmaRows + (p.pairs < p.experts ? p.pairs : p.experts);
+    const int cols = gated ? kMmaWeightRows / 2 : kMmaWeightRows;
+    const int64_t col_tiles = (p.n + cols - 1) / cols;
+    if (row_tiles > 65535 || col_tiles > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+    const dim3 grid((unsigned)col_tiles, (unsigned)row_tiles);
+    if (gated) return (int)launch_chain(moe_gemm_mma_kernel<true>, grid, dim3(256), 0, stream, dim3(1, 1, 1), p);
+    return (int)launch_chain(moe_gemm_mma_kernel<false>, grid, dim3(256), 0, stream, dim3(1, 1, 1), p);
+  }
   // every expert may end in a tile that is not full
   const int64_t row_tiles = p.pairs / kTileRows + (p.pairs < p.experts ? p.pairs : p.experts);
   const int64_t col_tiles = (p.n + kTileCols - 1) / kTileCols;

@@ -523,22 +523,30 @@ def moe_sort(chosen, experts: int):
     return order, offsets
 
 
-def moe_gate_up(x, w_gate_up, order, offsets, *, top, limit, slope):
+def moe_gate_up(x, w_gate_up, order, offsets, *, top, limit, slope, kernel: str = "auto"):
     """Row r of the result belongs to pair ``order[r]`` and is its expert's ``g * sigmoid(slope * g) * (u + 1)`` with
     ``g = min(W_gate x, limit)``, ``u = clamp(W_up x, -limit, limit)`` for the pair's token;
-    ``w_gate_up`` [experts, gate rows then up rows, hidden].  [tokens * top, intermediate] in the dtype of ``x``."""
+    ``w_gate_up`` [experts, gate rows then up rows, hidden].  [tokens * top, intermediate] in the dtype of ``x``.
+    ``kernel``: ``"auto"`` takes the tensor cores (mma.sync) for bfloat16 with a hidden size that is a multiple of
+    eight, ``"plain"`` keeps the float-arithmetic form, which is also all of float32."""
     inter = w_gate_up.shape[1] // 2
     act = torch.empty((order.numel(), inter), dtype=x.dtype, device=x.device)
-    ext().moe_gate_up(x, w_gate_up, order, offsets, act, top, float(limit), float(slope))
+    if kernel == "plain":
+        ext().moe_gate_up(x, w_gate_up, order, offsets, act, top, float(limit), float(slope), True)
+    else:
+        ext().moe_gate_up(x, w_gate_up, order, offsets, act, top, float(limit), float(slope))
     _launched()
     return act
 
 
-def moe_down(act, w_down, order, offsets, weights):
+def moe_down(act, w_down, order, offsets, weights, kernel: str = "auto"):
     """``weights[pair] * W_down[expert] act[r]`` for every sorted row r, written to row ``order[r]`` of a float32
-    [tokens * top, hidden]."""
+    [tokens * top, hidden].  ``kernel`` as for :func:`moe_gate_up`."""
     out = torch.empty((order.numel(), w_down.shape[1]), dtype=torch.float32, device=act.device)
-    ext().moe_down(act, w_down, order, offsets, weights, out)
+    if kernel == "plain":
+        ext().moe_down(act, w_down, order, offsets, weights, out, True)
+    else:
+        ext().moe_down(act, w_down, order, offsets, weights, out)
     _launched()
     return out
 

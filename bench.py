@@ -1,6 +1,6 @@
 """Benchmark of the engine on one B200: decode tokens per second at the Qwen3-8B shape.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference] [--shape 8b|14b|32b|sukalorn]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference] [--shape 8b|14b|32b|sukalorn|zifuzen]
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch through the engine's own step
 function (every kernel of the model and the token choice); ``value`` is batch / step time, timed with CUDA
@@ -9,6 +9,7 @@ step copies that step's token ids and index data from pinned host memory to the 
 chosen tokens back.  ``prefill`` is one 2,048-token prompt in one step; ``points`` holds decode at batch 1
 and 64; ``roofline`` compares the bytes a decode step must read (every weight once, the live requests'
 cache) with the copy bandwidth.  Weights are random (seeded), token ids synthetic (seeded uniform).
+``--shape zifuzen`` does for the Zifuzen design what ``--shape sukalorn`` does for Sukalorn.
 ``--shape sukalorn`` prints a line of its own: prefill and decode of four Sukalorn layers at two sizes beside Qwen3
 layers of equal size, and the attention kernels alone.
 Between timed steps nothing is flushed: every step streams the whole model (16 GB at full depth) through
@@ -458,6 +459,9 @@ SUKALORN_SIZES = {
 }
 SUKALORN_VOCAB = 32000
 SUKALORN_LAYERS = 4
+#: float32 multiply-adds of the CUDA cores, the pipe a recurrence kept in 32-bit runs on: 148 SMs x 128 lanes x 2 FLOPs
+#: at the 1,965 MHz the clocks show under load
+FP32_FMA_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
 
 
 def sukalorn_config(z: dict, layers: int) -> dict:
@@ -478,12 +482,48 @@ def qwen3_like(z: dict, layers: int) -> dict:
                 vocab_size=SUKALORN_VOCAB)
 
 
-def sukalorn_shape(args) -> int:
+# Zifuzen at sizes that resemble a real model's layers: four layers (delta + routed experts, attention + dense,
+# delta_2 + routed experts, attention on the second layer's pages + routed experts), beside Qwen3 layers of the same
+# width, heads, head size and dense feed-forward width.  A token's routed experts and the shared one together are as
+# wide as half the dense feed-forward.
+ZIFUZEN_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, delta_heads=16, delta_qk_heads=4, conv=4,
+               experts=32, top=4, expert_ff=768, shared_ff=1024, groups=(8, 4)),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, delta_heads=32, delta_qk_heads=8, conv=4,
+               experts=64, top=4, expert_ff=1024, shared_ff=2048, groups=(8, 4)),
+}
+
+
+def zifuzen_config(z: dict, layers: int) -> dict:
+    attention = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                 "scale": z["dim"] ** -0.5}
+    delta = {"heads": z["delta_heads"], "kv_heads": z["delta_qk_heads"], "dim": z["dim"], "vdim": z["dim"],
+             "conv": z["conv"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5,
+                      "groups": {"count": z["groups"][0], "keep": z["groups"][1]}},
+           "shared": {"ff": z["shared_ff"], "limit": 7.0}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    pattern = [("delta", delta, moe), ("attention", attention, dense), ("delta_2", delta, moe),
+               ("attention", dict(attention, kv_from=1), moe)]
+    out = []
+    for i in range(layers):
+        kind, mixer, mlp = pattern[i % 4]
+        mixer = dict(mixer)
+        if "kv_from" in mixer:
+            mixer["kv_from"] = i - 2
+        out.append({"type": kind, "mixer": mixer, "mlp": json.loads(json.dumps(mlp))})
+    return {"architecture": "Zifuzen", "vocab": SUKALORN_VOCAB, "width": z["width"], "max_positions": CONTEXT,
+            "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": out}
+
+
+def sukalorn_shape(args, design: str = "sukalorn") -> int:
     """Prefill (one 2,048-token prompt) and decode (batch 8 from 1,024-token prompts) of the Sukalorn design at two
     layer sizes, each beside Qwen3 layers of the same width, heads, head size and feed-forward width, through the
     engine's own step function; then the attention kernels alone at the same shapes, each with the fraction of the
     measured peak it reaches (prompt: FLOPs over the burst bf16 product peak; decode: cache bytes over the copy
-    bandwidth).  ``value`` is Sukalorn's decode tokens per second at the larger size."""
+    bandwidth).  ``value`` is Sukalorn's decode tokens per second at the larger size.  ``design="zifuzen"``: the same
+    for the Zifuzen design, with its delta-rule and routed-expert kernels alone."""
     import torch
     from ampere_kv_engine_b200.config.engine_config import EngineConfig
     from ampere_kv_engine_b200.engine.batch import SeqStep
@@ -626,7 +666,107 @@ def sukalorn_shape(args) -> int:
                 out[f"{name}_{case}"] = entry
         return out
 
+    def zifuzen_kernels_alone(z: dict) -> dict:
+        """The delta rule's scan and the routed experts' grouped products by themselves at this size: a 2,048-token
+        prompt as one sequence, and single tokens of `batch` sequences."""
+        out = {}
+        H, G, D, taps = z["delta_heads"], z["delta_qk_heads"], z["dim"], z["conv"]
+        V = D
+        channels = 2 * G * D + H * V
+        memory = H * D * V
+        g = torch.Generator(device=device).manual_seed(2)
+        state = torch.zeros((batch + 1, memory + (taps - 1) * channels), device=device)
+        conv = torch.rand((channels, taps), device=device, generator=g) - 0.3
+        rate_log = torch.full((H,), -3.0, device=device)
+        zeros_h, ones_v = torch.zeros((H,), device=device), torch.ones((V,), device=device)
+        sizes_kw = dict(num_heads=H, num_kv_heads=G, head_dim=D, v_dim=V, taps=taps)
+        dev = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+        fp32_peak = peaks.get("fp32_tflops") or FP32_FMA_TFLOPS
+        for name, lens in (("prompt", [PREFILL_TOKENS]), ("decode", [1] * batch)):
+            tokens = sum(lens)
+            cu, slots = dev([0] + [sum(lens[:i + 1]) for i in range(len(lens))]), dev(list(range(len(lens))))
+            x = torch.randn((tokens, channels + H * V + 2 * H), device=device, generator=g).to(torch.bfloat16)
+            prep = lambda: ops.delta_prep(x, conv, rate_log, zeros_h, state, cu, slots, unit_eps=1e-6, **sizes_kw)
+            qkv, coef = prep()
+            scan = lambda: ops.delta_scan(qkv, coef, x, ones_v, state, cu, slots, norm_eps=1e-6, **sizes_kw)
+            for case, fn in (("delta_prep", prep), ("delta_scan", scan)):
+                for _ in range(3):
+                    fn()
+                ms = timed(fn, 5, flush_l2=True)
+                entry = {"ms": round(ms, 4)}
+                if case == "delta_scan":
+                    flops = 7.0 * tokens * H * D * V          # decay, two products and the rank-one update per token
+                    moved = 2.0 * 4 * len(lens) * memory + 4.0 * tokens * (channels + 2 * H * V)
+                    entry.update(tflops=round(flops / (ms / 1000) / 1e12, 3),
+                                 frac_of_fp32_fma_peak=round(flops / (ms / 1000) / 1e12 / fp32_peak, 4),
+                                 state_gbs=round(moved / (ms / 1000) / 1e9, 1),
+                                 frac_of_hbm=round(moved / (ms / 1000) / 1e9 / peaks["hbm_gbs"], 4))
+                out[f"{name}_{case}"] = entry
+            # the routed experts: router, choice, sort, both grouped products, the sum
+            E, top, F, W = z["experts"], z["top"], z["expert_ff"], z["width"]
+            xs = torch.randn((tokens, W), device=device, generator=g).to(torch.bfloat16)
+            w_gu = (torch.randn((E, 2 * F, W), device=device, generator=g) * 0.02).to(torch.bfloat16)
+            w_d = (torch.randn((E, W, F), device=device, generator=g) * 0.02).to(torch.bfloat16)
+            logits = torch.randn((tokens, E), device=device, generator=g)
+            route = lambda: ops.moe_route(logits, None, top=top, groups=z["groups"][0], keep_groups=z["groups"][1],
+                                          group_top=2, scale=2.5, weight_eps=1e-20)
+            chosen, weights = route()
+            sort = lambda: ops.moe_sort(chosen, E)
+            order, offsets = sort()
+            gate_up = lambda: ops.moe_gate_up(xs, w_gu, order, offsets, top=top, limit=7.0, slope=1.702)
+            act = gate_up()
+            down = lambda: ops.moe_down(act, w_d, order, offsets, weights)
+            parts = down()
+            used = int((offsets[1:] > offsets[:-1]).sum())
+            for case, fn, flops, moved in (
+                    ("moe_route", route, 0.0, 4.0 * tokens * E), ("moe_sort", sort, 0.0, 8.0 * tokens * top),
+                    ("moe_gate_up", gate_up, 4.0 * tokens * top * F * W, 2.0 * used * 2 * F * W),
+                    ("moe_down", down, 2.0 * tokens * top * F * W, 2.0 * used * F * W),
+                    ("moe_combine", lambda: ops.moe_combine(parts, None, top=top), 0.0, 4.0 * tokens * (top + 1) * W)):
+                for _ in range(3):
+                    fn()
+                ms = timed(fn, 5, flush_l2=True)
+                entry = {"ms": round(ms, 4)}
+                if flops:
+                    entry.update(tflops=round(flops / (ms / 1000) / 1e12, 2),
+                                 frac_of_bf16_peak=round(flops / (ms / 1000) / 1e12 / peaks["bf16_tflops"], 4),
+                                 weight_gbs=round(moved / (ms / 1000) / 1e9, 1),
+                                 frac_of_hbm=round(moved / (ms / 1000) / 1e9 / peaks["hbm_gbs"], 4))
+                out[f"{name}_{case}"] = entry
+            # the library product of the same FLOPs as one dense matrix, for scale
+            dense_w = w_gu.view(-1, W)[:2 * F * top] if name == "prompt" else None
+            if dense_w is not None:
+                fn = lambda: torch.nn.functional.linear(xs, dense_w)
+                for _ in range(3):
+                    fn()
+                ms = timed(fn, 5, flush_l2=True)
+                flops = 2.0 * tokens * dense_w.shape[0] * W
+                out["prompt_library_product_of_equal_flops"] = {
+                    "ms": round(ms, 4), "tflops": round(flops / (ms / 1000) / 1e12, 2),
+                    "frac_of_bf16_peak": round(flops / (ms / 1000) / 1e12 / peaks["bf16_tflops"], 4)}
+        return out
+
     sizes = {}
+    if design == "zifuzen":
+        with ClockSampler() as clocks:
+            for name, z in ZIFUZEN_SIZES.items():
+                sizes[name] = {"zifuzen": measure(zifuzen_config(z, layers)), "qwen3": measure(qwen3_like(z, layers)),
+                               "kernels": zifuzen_kernels_alone(z)}
+        head = sizes["4k"]["zifuzen"]
+        line = {"metric": "decode tok/s at batch 8 of four Zifuzen layers (width 4,096, B200); prefill, a smaller size, "
+                          "Qwen3 layers of equal size and the delta-rule and routed-expert kernels alone alongside",
+                "value": head["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": head["decode_ms"], "higher_is_better": True, "dtype": "bf16",
+                "data": "synthetic (seeded uniform token ids, seeded random weights)",
+                "config": {"model": "Zifuzen", "layers": layers, "sizes": ZIFUZEN_SIZES, "vocab": SUKALORN_VOCAB,
+                           "global_batch": batch, "prompt_len": PROMPT_LEN, "prefill_tokens": PREFILL_TOKENS,
+                           "page_size": args.page_size, "l2": "whole steps: inputs larger than L2; kernels alone: L2 "
+                           "flushed (a 256 MB write) before every timed launch", "peaks": peaks["source"],
+                           "fp32_fma_tflops": FP32_FMA_TFLOPS},
+                "gpu_launches": head["launches_per_decode_step"] * args.steps, "sizes": sizes,
+                "clocks": clocks.summary()}
+        print(json.dumps(line))
+        return 0
     with ClockSampler() as clocks:
         for name, z in SUKALORN_SIZES.items():
             sizes[name] = {"sukalorn": measure(sukalorn_config(z, layers)), "qwen3": measure(qwen3_like(z, layers)),
@@ -653,17 +793,18 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page (a power of two, 16 or more)")
-    parser.add_argument("--shape", choices=sorted(SHAPES) + ["sukalorn"], default="8b",
+    parser.add_argument("--shape", choices=sorted(SHAPES) + ["sukalorn", "zifuzen"], default="8b",
                         help="8b: the headline benchmark; 14b: a mixed scheduler load of 64 requests; 32b: long-context "
                              "decode at batch 16; sukalorn: prefill and decode of the Sukalorn design at two layer "
-                             "sizes beside Qwen3 layers of equal size (each prints its own one line)")
+                             "sizes beside Qwen3 layers of equal size; zifuzen: the same for the Zifuzen design (each prints "
+                             "its own one line)")
     parser.add_argument("--layers", type=int, default=None,
                         help="run fewer layers of the same sizes (reported in config beside the full count)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
     args = parser.parse_args()
 
-    if args.shape == "sukalorn":
+    if args.shape in ("sukalorn", "zifuzen"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference arm runs the 8b shape only"}))
             return 0
@@ -671,7 +812,7 @@ def main() -> int:
             print(json.dumps({"error": "this engine runs on one GPU; --gpus must be 1", "n_gpus": args.gpus}))
             return 2
         args.warmup = max(3, args.warmup)
-        return sukalorn_shape(args)
+        return sukalorn_shape(args, design=args.shape)
     if args.layers is None:
         args.layers = SHAPES[args.shape]["num_hidden_layers"]
     if args.impl == "reference":

@@ -380,7 +380,7 @@ class FakeExt:
         offsets[0] = 0
         offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
 
-    def moe_gate_up(self, x, w_gate_up, order, offsets, act, top, limit, slope):
+    def moe_gate_up(self, x, w_gate_up, order, offsets, act, top, limit, slope, plain=False):
         inter = w_gate_up.shape[1] // 2
         off = offsets.tolist()
         for e in range(len(off) - 1):
@@ -391,7 +391,7 @@ class FakeExt:
             g, u = both[:, :inter].clamp(max=limit), both[:, inter:].clamp(min=-limit, max=limit)
             act[off[e]:off[e + 1]] = (g * torch.sigmoid(slope * g) * (u + 1)).to(act.dtype)
 
-    def moe_down(self, act, w_down, order, offsets, weights, out):
+    def moe_down(self, act, w_down, order, offsets, weights, out, plain=False):
         off = offsets.tolist()
         flat = weights.reshape(-1)
         for e in range(len(off) - 1):

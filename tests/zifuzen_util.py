@@ -87,7 +87,7 @@ Z3 = {
         _layer("delta", _delta(4, 2, 128, 128, 4), _moe(8, 2, 128, 2.0, 1.0, groups=(4, 2), shared=(192, 2.0))),
         _layer("attention", _attention(4, 2, 128, 128, 0.09), 512),
         _layer("delta_2", _delta(8, 8, 64, 32, 3), None),
-        _layer("attention", _attention(8, 2, 128, 128, 0.09, kv_from=1), _moe(16, 3, 64, 1.0, 2.0)),
+        _layer("attention", _attention(8, 2, 128, 128, 0.09, kv_from=1), _moe(6, 2, 64, 1.0, 2.0)),
         _layer("attention", _attention(8, 1, 64, 64, 0.12), 384),
     ],
 }
@@ -141,7 +141,7 @@ def plain_logits(folder: str, raw: dict, requests: dict[str, list[int]]) -> dict
     return {rid: plain.forward(raw, w, toks).float() for rid, toks in requests.items()}
 
 
-def decisive_requests(folder: str, raw: dict, lengths, seed: int, margin: float = 0.03, tries: int = 400
+def decisive_requests(folder: str, raw: dict, lengths, seed: int, margin: float = 0.02, tries: int = 400
                       ) -> dict[str, list[int]]:
     """Random requests of the given lengths in which no expert choice is a close call: for every token and routed
     layer the chosen experts (and kept groups) lead the others by at least ``margin`` in the plain implementation, so
@@ -155,7 +155,7 @@ def decisive_requests(folder: str, raw: dict, lengths, seed: int, margin: float 
         toks: list[int] = []
         while len(toks) < n:
             for _ in range(tries):
-                cand = toks + torch.randint(0, raw["vocab"], (min(8, n - len(toks)),), generator=g).tolist()
+                cand = toks + torch.randint(0, raw["vocab"], (min(4, n - len(toks)),), generator=g).tolist()
                 margins: list = []
                 if routed:
                     plain.forward(raw, w, cand, margins=margins)
