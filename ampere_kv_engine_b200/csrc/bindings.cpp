@@ -1014,6 +1014,40 @@ void branch_layernorm(Tensor& hidden, const Tensor& branch, const Tensor& weight
                "branch_layernorm");
 }
 
+void branch_layernorm_parts(Tensor& hidden, const Tensor& parts, const OptTensor& shared, const Tensor& weight,
+                            const OptTensor& copy, double eps, int64_t top) {
+  check_cuda(hidden, "hidden");
+  AKV_CHECK(hidden.scalar_type() == at::kFloat && hidden.dim() == 2, "hidden must be float32 [tokens, hidden]");
+  const int64_t n = hidden.size(0), h = hidden.size(1);
+  check_f32(weight, "weight", h);
+  AKV_CHECK(top >= 1, "top must be positive");
+  check_f32(parts, "parts", n * top * h);
+  AKV_CHECK(parts.device() == hidden.device(), "parts must be on the stream's device");
+  AKV_CHECK(h * 4 <= 200 * 1024, "branch_layernorm_parts: hidden size ", h, " exceeds the kernel's limit of 51200");
+  const void* shared_ptr = nullptr;
+  int shared_code = 0;
+  if (shared.has_value()) {
+    check_cuda(*shared, "shared");
+    AKV_CHECK(shared->numel() == n * h && shared->device() == hidden.device(), "shared must be [tokens, hidden]");
+    shared_ptr = shared->data_ptr();
+    shared_code = dtype_code(*shared, "shared");
+  }
+  void* copy_ptr = nullptr;
+  int copy_code = 0;
+  if (copy.has_value()) {
+    check_cuda(*copy, "copy");
+    AKV_CHECK(copy->scalar_type() == at::kBFloat16 && copy->numel() == n * h && copy->device() == hidden.device(),
+              "copy must be bfloat16 [tokens, hidden]");
+    copy_ptr = copy->data_ptr();
+    copy_code = 1;
+  }
+  c10::cuda::CUDAGuard guard(hidden.device());
+  check_launch(akv::launch_branch_layernorm_parts(hidden.data_ptr<float>(), parts.data_ptr<float>(), (int)top, shared_ptr,
+                                                  shared_code, weight.data_ptr<float>(), copy_ptr, copy_code, n, h,
+                                                  (float)eps, stream_of(hidden)),
+               "branch_layernorm_parts");
+}
+
 void stream_copy(const Tensor& hidden, Tensor& out) {
   check_cuda(hidden, "hidden");
   check_cuda(out, "out");
@@ -1061,11 +1095,11 @@ akv::DeltaParams delta_params(const Tensor& x, const Tensor& state, const Tensor
   const int64_t channels = 2 * num_kv_heads * head_dim + num_heads * v_dim;
   const int64_t width = channels + num_heads * v_dim + 2 * num_heads;
   AKV_CHECK(x.dim() == 2 && x.size(1) == width, "x must be [tokens, ", width, "]: q, k, v, gate, beta, step");
-  const int64_t memory = num_heads * head_dim * v_dim;
+  const int64_t memory = akv::delta_memory_floats((int)num_heads, (int)head_dim, (int)v_dim);
+  const int64_t floats = (memory + (taps - 1) * channels + 3) / 4 * 4;
   check_cuda(state, "state");
-  AKV_CHECK(state.scalar_type() == at::kFloat && state.dim() == 2 && state.size(1) == memory + (taps - 1) * channels &&
-                state.device() == x.device(),
-            "state must be float32 [slots, ", memory + (taps - 1) * channels, "]");
+  AKV_CHECK(state.scalar_type() == at::kFloat && state.dim() == 2 && state.size(1) == floats && state.device() == x.device(),
+            "state must be float32 [slots, ", floats, "]");
   check_i32(cu_q, "cu_q", 1);
   const int64_t num_seqs = cu_q.numel() - 1;
   check_i32(state_slots, "state_slots", num_seqs);
@@ -1177,7 +1211,7 @@ void moe_sort(const Tensor& chosen, Tensor& order, Tensor& offsets) {
 }
 
 void moe_gate_up(const Tensor& x, const Tensor& w, const Tensor& order, const Tensor& offsets, Tensor& act, int64_t top,
-                 double limit, double slope, bool plain) {
+                 double limit, double slope, int64_t form) {
   check_cuda(x, "x");
   check_cuda(w, "w");
   check_cuda(act, "act");
@@ -1204,13 +1238,14 @@ void moe_gate_up(const Tensor& x, const Tensor& w, const Tensor& order, const Te
   p.limit = (float)limit;
   p.slope = (float)slope;
   p.dtype = dtype_code(x, "x");
-  p.force_plain = plain ? 1 : 0;
+  AKV_CHECK(form >= 0 && form <= 3, "form: 0 by size, 1 float arithmetic, 2 mma.sync tiles, 3 few rows");
+  p.force_plain = (int)form;
   c10::cuda::CUDAGuard guard(x.device());
   check_launch(akv::launch_moe_gemm(p, true, stream_of(x)), "moe_gate_up");
 }
 
 void moe_down(const Tensor& act, const Tensor& w, const Tensor& order, const Tensor& offsets, const Tensor& weights,
-              Tensor& out, bool plain) {
+              Tensor& out, int64_t form) {
   check_cuda(act, "act");
   check_cuda(w, "w");
   check_same(act, w, "act", "w");
@@ -1234,7 +1269,8 @@ void moe_down(const Tensor& act, const Tensor& w, const Tensor& order, const Ten
   p.n = (int)hidden;
   p.top = 1;
   p.dtype = dtype_code(act, "act");
-  p.force_plain = plain ? 1 : 0;
+  AKV_CHECK(form >= 0 && form <= 3, "form: 0 by size, 1 float arithmetic, 2 mma.sync tiles, 3 few rows");
+  p.force_plain = (int)form;
   c10::cuda::CUDAGuard guard(act.device());
   check_launch(akv::launch_moe_gemm(p, false, stream_of(act)), "moe_down");
 }
@@ -1347,6 +1383,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("rows"), py::arg("eps"), py::arg("status") = py::none());
   m.def("branch_layernorm", &branch_layernorm, py::arg("hidden"), py::arg("branch"), py::arg("weight"), py::arg("copy"),
         py::arg("eps"));
+  m.def("branch_layernorm_parts", &branch_layernorm_parts, py::arg("hidden"), py::arg("parts"), py::arg("shared"),
+        py::arg("weight"), py::arg("copy"), py::arg("eps"), py::arg("top"));
   m.def("stream_copy", &stream_copy, py::arg("hidden"), py::arg("out"));
   m.def("glu", &glu, py::arg("gate_up"), py::arg("out"), py::arg("kind"), py::arg("block") = 0, py::arg("limit") = 0.0,
         py::arg("slope") = 1.0);
@@ -1358,13 +1396,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("cu_q"), py::arg("state_slots"), py::arg("scratch"), py::arg("out"), py::arg("num_heads"),
         py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("v_dim"), py::arg("taps"), py::arg("norm_eps"));
   m.def("delta_scan_supported", [](int64_t dim, int64_t v_dim) { return akv::delta_scan_supported((int)dim, (int)v_dim); });
+  m.def("delta_memory_floats", [](int64_t heads, int64_t dim, int64_t v_dim) {
+    return akv::delta_memory_floats((int)heads, (int)dim, (int)v_dim);
+  });
   m.def("moe_route", &moe_route, py::arg("logits"), py::arg("correction"), py::arg("chosen"), py::arg("weights"),
         py::arg("groups"), py::arg("keep_groups"), py::arg("group_top"), py::arg("scale"), py::arg("weight_eps"));
   m.def("moe_sort", &moe_sort, py::arg("chosen"), py::arg("order"), py::arg("offsets"));
   m.def("moe_gate_up", &moe_gate_up, py::arg("x"), py::arg("w"), py::arg("order"), py::arg("offsets"), py::arg("act"),
-        py::arg("top"), py::arg("limit"), py::arg("slope"), py::arg("plain") = false);
+        py::arg("top"), py::arg("limit"), py::arg("slope"), py::arg("form") = 0);
   m.def("moe_down", &moe_down, py::arg("act"), py::arg("w"), py::arg("order"), py::arg("offsets"), py::arg("weights"),
-        py::arg("out"), py::arg("plain") = false);
+        py::arg("out"), py::arg("form") = 0);
   m.def("moe_combine", &moe_combine, py::arg("parts"), py::arg("shared"), py::arg("out"), py::arg("top"));
   m.def("paged_attention", &paged_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"),
         py::arg("block_table"), py::arg("cu_q"), py::arg("ctx_lens"), py::arg("tile_seq"), py::arg("tile_q0"),

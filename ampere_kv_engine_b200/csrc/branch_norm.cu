@@ -4,6 +4,7 @@
 //                      (x - mean) / sqrt(var + eps) * w with var = mean((x - mean)^2).
 //   branch_layernorm:  hidden += LayerNorm(branch): the norm sits on the branch's output and its result is what
 //                      joins the float32 residual stream; optionally the new stream rounded to the compute dtype.
+//                      The branch may also come as the rows of routed experts that are still to be added up.
 //   stream_copy:       the float32 stream rounded to the compute dtype (what the first branch of a model reads).
 //   glu:               act(gate) * up with the tanh form of GELU, SiLU, or the clamped form
 //                      g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(slope * g) * (u + 1).
@@ -148,6 +149,64 @@ int launch_branch_layernorm(float* hidden, const void* branch, int branch_dtype,
   if (bf_copy)
     return launch(branch_layernorm_kernel<float, __nv_bfloat16>, (const float*)branch, (__nv_bfloat16*)copy);
   return launch(branch_layernorm_kernel<float, float>, (const float*)branch, (float*)nullptr);
+}
+
+// The same with the branch given as float32 rows that are still to be added up: row t of the branch is
+// parts[t * top], ..., parts[t * top + top - 1] in that order, plus shared[t] (or nothing).
+template <typename TS, typename TC>
+__global__ void branch_layernorm_parts_kernel(float* __restrict__ hidden, const float* __restrict__ parts, int top,
+                                              const TS* __restrict__ shared, const float* __restrict__ weight,
+                                              TC* __restrict__ copy, int64_t hidden_size, float eps) {
+  __shared__ float scratch[33];
+  extern __shared__ float row_cache[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const float* first = parts + row * top * hidden_size;
+  float sum = 0.f;
+  for (int64_t i = threadIdx.x; i < hidden_size; i += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < top; ++s) v += first[s * hidden_size + i];
+    if (shared != nullptr) v += to_float<TS>(shared[row * hidden_size + i]);
+    row_cache[i] = v;
+    sum += v;
+  }
+  float mean, inv;
+  row_moments(row_cache, hidden_size, sum, eps, scratch, mean, inv);
+  float* h = hidden + row * hidden_size;
+  for (int64_t i = threadIdx.x; i < hidden_size; i += blockDim.x) {
+    const float v = h[i] + (row_cache[i] - mean) * inv * weight[i];
+    h[i] = v;
+    if (copy != nullptr) copy[row * hidden_size + i] = from_float<TC>(v);
+  }
+}
+
+int launch_branch_layernorm_parts(float* hidden, const float* parts, int top, const void* shared, int shared_dtype,
+                                  const float* weight, void* copy, int copy_dtype, int64_t num_tokens,
+                                  int64_t hidden_size, float eps, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  const size_t smem = (size_t)hidden_size * sizeof(float);
+  if (smem > 200 * 1024 || top < 1) return (int)cudaErrorInvalidValue;
+  const int threads = row_threads(hidden_size);
+  auto launch = [&](auto kernel, auto* typed_shared, auto* typed_copy) {
+    if (smem > 48 * 1024) {
+      cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return (int)err;
+    }
+    return (int)launch_chain(kernel, dim3((unsigned)num_tokens), dim3(threads), smem, stream, dim3(1, 1, 1), hidden,
+                             parts, top, typed_shared, weight, typed_copy, hidden_size, eps);
+  };
+  const bool bf_copy = copy != nullptr && copy_dtype == kBFloat16;
+  if (copy != nullptr && !bf_copy) return (int)cudaErrorInvalidValue;
+  if (shared != nullptr && shared_dtype == kBFloat16) {
+    if (bf_copy)
+      return launch(branch_layernorm_parts_kernel<__nv_bfloat16, __nv_bfloat16>, (const __nv_bfloat16*)shared,
+                    (__nv_bfloat16*)copy);
+    return launch(branch_layernorm_parts_kernel<__nv_bfloat16, float>, (const __nv_bfloat16*)shared, (float*)nullptr);
+  }
+  if (bf_copy)
+    return launch(branch_layernorm_parts_kernel<float, __nv_bfloat16>, (const float*)shared, (__nv_bfloat16*)copy);
+  return launch(branch_layernorm_parts_kernel<float, float>, (const float*)shared, (float*)nullptr);
 }
 
 __global__ void stream_copy_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, int64_t total) {

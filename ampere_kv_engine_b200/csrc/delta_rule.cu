@@ -5,14 +5,13 @@
 //                from the request's state slot) and SiLU; q and k heads become unit vectors (q also times
 //                dim^-1/2); beta = sigmoid(.), decay = exp(-exp(rate_log) * softplus(step + step_bias)).
 //                Everything it writes is float32.  One warp per (token, head).
-//   delta_scan:  one block per (sequence, head) walks the step's tokens of that sequence in order:
-//                S *= decay;  u = beta (v - S^T k);  S += k u^T;  o = S^T q.
-//                A thread group of L lanes owns one value column of S (dim / L elements per lane, in registers for
-//                the whole step); the two products are EPT multiply-adds per lane and a shuffle reduction over the
-//                group; the next token's q, k, v, beta, decay are fetched while the current one is computed, so a
-//                token costs one block barrier.  Afterwards the block's warps apply the output norm
-//                o / sqrt(mean(o^2) + eps) * w * silu(gate) to the tokens in parallel, and the block of head 0 moves
-//                the sequence's last taps - 1 convolution inputs into the state.
+//   delta_scan:  blocks per (sequence, head, slice of the value columns) walk the step's tokens of that sequence in
+//                order:  S *= decay;  u = beta (v - S^T k);  S += k u^T;  o = S^T q.
+//                A thread group of up to 8 lanes owns one value column of S (in registers for the whole step); the
+//                two products are a few multiply-adds per lane and a shuffle reduction over the group; tokens are
+//                staged through shared memory in chunks, so a token costs no block barrier.  A second kernel applies
+//                the output norm o / sqrt(mean(o^2) + eps) * w * silu(gate) to all tokens in parallel, a third moves
+//                each sequence's last taps - 1 convolution inputs into the state.
 //
 // The walk is token by token whatever the step holds, so the state after a token does not depend on how the
 // tokens were cut into steps.  A sequence whose state slot is negative (padding of a captured step) is left alone
@@ -130,202 +129,286 @@ int launch_delta_prep(const DeltaParams& p, cudaStream_t stream) {
   return (int)launch_chain(delta_prep_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, dim3(1, 1, 1), p);
 }
 
-// Shared memory of the scan, per buffer: q and k (each lane's EPT elements padded by four floats, so that the lanes
-// of a group read different banks), v, beta and decay.
-template <int EPT>
-struct ScanLayout {
-  static constexpr int kPitch = EPT + 4;
-  __host__ __device__ static int vec(int lanes) { return lanes * kPitch; }
-  // a multiple of four floats, so that the second buffer's rows can be read as float4 too
-  __host__ __device__ static int floats(int lanes, int v_dim) { return (2 * vec(lanes) + v_dim + 2 + 3) / 4 * 4; }
+// ---------------------------------------------------------------------------------------------------------
+// The scan.  A block owns `cols` value columns of one head of one sequence; a group of `lanes` (up to 8) lanes owns
+// a column, each lane EPT consecutive elements of the dim, in registers for the whole step.  Tokens are staged in
+// chunks: while the block walks the tokens of one chunk out of shared memory (no barrier between tokens: all a
+// token needs from other threads is two shuffle reductions inside its lane group), the next chunk's q, k, v, beta
+// and decay are already under way from global memory.
+//
+// S in the state slot, per head: element (column, lane, e) at ((e / 4) * (v_dim * lanes) + column * lanes + lane) * 4
+// + e % 4, so that a warp's float4 accesses are consecutive; a head takes v_dim * lanes * EPT floats.
+namespace {
+
+struct ScanShape {
+  int ept, lanes, cols, threads, chunk;   // elements per lane, lanes per column, columns and threads per block, tokens per chunk
 };
 
-template <typename T, int EPT>
-__global__ void __launch_bounds__(EPT <= 32 ? 1024 : (EPT <= 64 ? 512 : 256)) delta_scan_kernel(DeltaParams p, int lanes) {
+constexpr int kScanFetch = 24;      // registers a thread may hold of the chunk under way
+
+// floats of one staged token in shared memory: q and k (each lane's elements padded by four floats), the block's v
+// columns, beta and decay; a multiple of four, so that every token's q and k can be read as float4
+__host__ __device__ inline int scan_token_floats(int lanes, int ept, int cols) {
+  return (2 * lanes * (ept + 4) + cols + 2 + 3) / 4 * 4;
+}
+
+__host__ __device__ inline int pow2_at_least(int n) {
+  int p = 1;
+  while (p < n) p *= 2;
+  return p;
+}
+
+// the smallest EPT of 4, 8, 16, 32 with which 8 lanes cover the dim; 256 threads a block
+inline ScanShape scan_shape(int dim, int v_dim) {
+  ScanShape s{0, 0, 0, 0, 0};
+  for (int e : {4, 8, 16, 32}) {
+    const int lanes = pow2_at_least((dim + e - 1) / e);
+    if (lanes <= 8) {
+      s.ept = e;
+      s.lanes = lanes;
+      break;
+    }
+  }
+  if (s.ept == 0) return s;
+  s.cols = 256 / s.lanes;
+  if (s.cols > v_dim) s.cols = v_dim;
+  s.threads = (s.cols * s.lanes + 31) / 32 * 32;
+  if (s.threads < 128) s.threads = 128;      // the fetch of a chunk is spread over the block (threads without a column idle)
+  // the largest chunk whose two buffers fit in 48 KB and whose fetch fits in the block's registers
+  const int per_token = scan_token_floats(s.lanes, s.ept, s.cols);
+  s.chunk = 16;
+  while (s.chunk > 1 && (2 * s.chunk * per_token * 4 > 48 * 1024 || s.chunk * (2 * dim + s.cols + 2) > kScanFetch * s.threads))
+    s.chunk /= 2;
+  return s;
+}
+
+}  // namespace
+
+bool delta_scan_supported(int dim, int v_dim) {
+  return dim > 0 && v_dim > 0 && dim <= kDeltaMaxDim && v_dim <= kDeltaMaxDim && scan_shape(dim, v_dim).ept != 0;
+}
+
+int64_t delta_memory_floats(int num_heads, int dim, int v_dim) {
+  const ScanShape s = scan_shape(dim, v_dim);
+  return (int64_t)num_heads * v_dim * s.lanes * s.ept;
+}
+
+template <int EPT>
+__global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p, int lanes, int cols, int chunk) {
   extern __shared__ __align__(16) float smem[];
-  using Layout = ScanLayout<EPT>;
+  constexpr int kPitch = EPT + 4;      // a lane's elements of q or k, padded: the lanes of a group read different banks
   pdl_launch_dependents();
   pdl_wait();
-  const int s = blockIdx.x, h = blockIdx.y;
+  const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols;
   const int G = p.num_kv_heads, H = p.num_heads, D = p.head_dim, V = p.v_dim;
   const int channels = 2 * G * D + H * V;
-  const int64_t width = (int64_t)channels + (int64_t)H * V + 2 * H;
   const int64_t first = p.cu_q[s];
   const int n = (int)(p.cu_q[s + 1] - first);
   const int slot = p.state_slots[s];
-  const T* x = (const T*)p.x;
-  T* out = (T*)p.out;
   if (n <= 0) return;
+  const int mine_cols = min(cols, V - col0);
+  float* scratch = p.scratch + first * H * V + (int64_t)h * V + col0;
   if (slot < 0 || slot >= p.num_slots) {
-    for (int64_t i = threadIdx.x; i < (int64_t)n * V; i += blockDim.x)
-      out[(first + i / V) * H * V + (int64_t)h * V + i % V] = from_float<T>(0.f);
+    for (int i = threadIdx.x; i < n * mine_cols; i += blockDim.x) scratch[(int64_t)(i / mine_cols) * H * V + i % mine_cols] = 0.f;
     return;
   }
   float* state = p.state + (int64_t)slot * p.state_stride;
   const int col = threadIdx.x / lanes, l = threadIdx.x % lanes;
-  const bool owner = col < V;
+  const bool owner = col < mine_cols;
   const int g = h / (H / G);
-  // this lane's part of the column: elements [l * EPT, l * EPT + EPT) of the dim
   float S[EPT];
-  float* mine = state + ((int64_t)h * V + col) * D + l * EPT;
+  float* mine = state + (int64_t)h * V * lanes * EPT + ((int64_t)(col0 + col) * lanes + l) * 4;
+  const int64_t quad_stride = (int64_t)V * lanes * 4;
 #pragma unroll
-  for (int e = 0; e < EPT; ++e) S[e] = (owner && l * EPT + e < D) ? mine[e] : 0.f;
+  for (int e = 0; e < EPT; e += 4) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (owner) v = *reinterpret_cast<const float4*>(mine + (e / 4) * quad_stride);
+    S[e] = v.x; S[e + 1] = v.y; S[e + 2] = v.z; S[e + 3] = v.w;
+  }
 
-  const int per_buffer = Layout::floats(lanes, V);
-  // what a thread fetches for the next token: entries idx = threadIdx.x + k * blockDim.x of [q | k | v | beta | decay]
-  const int fetch_total = 2 * D + V + 2;
-  constexpr int kFetch = 8;           // at most 2 * 256 + 256 + 2 entries over at least 128 threads
-  auto fetch = [&](int64_t token, float (&regs)[kFetch]) {
-    const float* qkv = p.qkv + token * channels;
-    const float* coef = p.coef + token * 2 * H;
+  const int vec = lanes * kPitch;                        // floats of one token's q (or k) in shared memory
+  const int per_token = scan_token_floats(lanes, EPT, cols);      // q, k, v of the block's columns, beta, decay
+  const int per_buffer = chunk * per_token;
+  const int fetch_per_token = 2 * D + mine_cols + 2;
+  // entry idx of a chunk: token idx / fetch_per_token, then [q | k | v | beta | decay]
+  auto fetch = [&](int t0, int count, float (&regs)[kScanFetch]) {
+    const int total = count * fetch_per_token;
 #pragma unroll
-    for (int k = 0; k < kFetch; ++k) {
-      const int idx = threadIdx.x + k * blockDim.x;
+    for (int r = 0; r < kScanFetch; ++r) {
+      const int idx = threadIdx.x + r * blockDim.x;
       float v = 0.f;
-      if (idx < D) v = qkv[g * D + idx];
-      else if (idx < 2 * D) v = qkv[G * D + g * D + (idx - D)];
-      else if (idx < 2 * D + V) v = qkv[2 * G * D + h * V + (idx - 2 * D)];
-      else if (idx == 2 * D + V) v = coef[h];
-      else if (idx == 2 * D + V + 1) v = coef[H + h];
-      regs[k] = v;
+      if (idx < total) {
+        const int t = idx / fetch_per_token, i = idx - t * fetch_per_token;
+        const float* qkv = p.qkv + (first + t0 + t) * channels;
+        const float* coef = p.coef + (first + t0 + t) * 2 * H;
+        if (i < D) v = qkv[g * D + i];
+        else if (i < 2 * D) v = qkv[G * D + g * D + (i - D)];
+        else if (i < 2 * D + mine_cols) v = qkv[2 * G * D + h * V + col0 + (i - 2 * D)];
+        else if (i == 2 * D + mine_cols) v = coef[h];
+        else v = coef[H + h];
+      }
+      regs[r] = v;
     }
   };
-  auto stash = [&](float* buffer, const float (&regs)[kFetch]) {
+  auto stash = [&](float* buffer, int count, const float (&regs)[kScanFetch]) {
+    const int total = count * fetch_per_token;
 #pragma unroll
-    for (int k = 0; k < kFetch; ++k) {
-      const int idx = threadIdx.x + k * blockDim.x;
-      if (idx < D) buffer[idx / EPT * Layout::kPitch + idx % EPT] = regs[k];
-      else if (idx < 2 * D) buffer[Layout::vec(lanes) + (idx - D) / EPT * Layout::kPitch + (idx - D) % EPT] = regs[k];
-      else if (idx < fetch_total) buffer[2 * Layout::vec(lanes) + (idx - 2 * D)] = regs[k];
-    }
-  };
-  // rows of q and k beyond dim stay zero in both buffers
-  for (int i = threadIdx.x; i < 2 * per_buffer; i += blockDim.x) smem[i] = 0.f;
-  __syncthreads();
-  float regs[kFetch];
-  fetch(first, regs);
-  stash(smem, regs);
-  __syncthreads();
-  float* scratch = p.scratch + first * H * V + (int64_t)h * V;
-  for (int t = 0; t < n; ++t) {
-    const float* buffer = smem + (t & 1) * per_buffer;
-    if (t + 1 < n) fetch(first + t + 1, regs);
-    const float* q = buffer + l * Layout::kPitch;
-    const float* k = buffer + Layout::vec(lanes) + l * Layout::kPitch;
-    const float* rest = buffer + 2 * Layout::vec(lanes);
-    const float v = owner ? rest[col] : 0.f;
-    const float beta = rest[V], decay = rest[V + 1];
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-    for (int e = 0; e < EPT; e += 4) {
-      const float4 kk = *reinterpret_cast<const float4*>(k + e);
-      S[e] *= decay; S[e + 1] *= decay; S[e + 2] *= decay; S[e + 3] *= decay;
-      a0 += S[e] * kk.x; a1 += S[e + 1] * kk.y; a2 += S[e + 2] * kk.z; a3 += S[e + 3] * kk.w;
-    }
-    float kv = (a0 + a1) + (a2 + a3);
-    for (int o = lanes >> 1; o > 0; o >>= 1) kv += __shfl_xor_sync(0xffffffffu, kv, o);
-    const float u = beta * (v - kv);
-    a0 = a1 = a2 = a3 = 0.f;
-#pragma unroll
-    for (int e = 0; e < EPT; e += 4) {
-      const float4 kk = *reinterpret_cast<const float4*>(k + e);
-      const float4 qq = *reinterpret_cast<const float4*>(q + e);
-      S[e] += kk.x * u; S[e + 1] += kk.y * u; S[e + 2] += kk.z * u; S[e + 3] += kk.w * u;
-      a0 += S[e] * qq.x; a1 += S[e + 1] * qq.y; a2 += S[e + 2] * qq.z; a3 += S[e + 3] * qq.w;
-    }
-    float o = (a0 + a1) + (a2 + a3);
-    for (int w = lanes >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-    if (owner && l == 0) scratch[(int64_t)t * H * V + col] = o;
-    if (t + 1 < n) stash(smem + ((t + 1) & 1) * per_buffer, regs);
-    __syncthreads();
-  }
-#pragma unroll
-  for (int e = 0; e < EPT; ++e)
-    if (owner && l * EPT + e < D) mine[e] = S[e];
-
-  // the output norm and gate, a warp per token (the raw outputs of this block are visible to it after the barrier)
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  const int64_t gate_first = (int64_t)channels + (int64_t)h * V;
-  for (int t = warp; t < n; t += warps) {
-    const float* raw = scratch + (int64_t)t * H * V;
-    float ss = 0.f;
-    for (int j = lane; j < V; j += 32) ss += raw[j] * raw[j];
-    const float inv = rsqrtf(warp_sum(ss) / (float)V + p.norm_eps);
-    const T* gate = x + (first + t) * width + gate_first;
-    T* dst = out + (first + t) * H * V + (int64_t)h * V;
-    for (int j = lane; j < V; j += 32) {
-      const float z = to_float<T>(gate[j]);
-      dst[j] = from_float<T>(raw[j] * inv * p.norm_weight[j] * (z / (1.f + expf(-z))));
-    }
-  }
-
-  // the convolutions' memory: the last taps - 1 inputs of [what was there before | this step's rows]
-  if (h == 0 && p.taps > 1) {
-    const int keep = p.taps - 1;
-    float* before = state + p.memory;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-      for (int i = 0; i < keep; ++i) {          // ascending: entry i reads entry i + n > i, not yet overwritten
-        const int back = n - keep + i;          // index within the step's tokens of this sequence
-        before[(int64_t)i * channels + c] = back >= 0 ? to_float<T>(x[(first + back) * width + c])
-                                                       : before[(int64_t)(i + n) * channels + c];
+    for (int r = 0; r < kScanFetch; ++r) {
+      const int idx = threadIdx.x + r * blockDim.x;
+      if (idx < total) {
+        const int t = idx / fetch_per_token, i = idx - t * fetch_per_token;
+        float* row = buffer + t * per_token;
+        if (i < D) row[i / EPT * kPitch + i % EPT] = regs[r];
+        else if (i < 2 * D) row[vec + (i - D) / EPT * kPitch + (i - D) % EPT] = regs[r];
+        else row[2 * vec + (i - 2 * D) + (i >= 2 * D + mine_cols ? cols - mine_cols : 0)] = regs[r];
       }
     }
+  };
+  // elements of q and k beyond the dim stay zero in both buffers
+  for (int i = threadIdx.x; i < 2 * per_buffer; i += blockDim.x) smem[i] = 0.f;
+  __syncthreads();
+  float regs[kScanFetch];
+  fetch(0, min(chunk, n), regs);
+  stash(smem, min(chunk, n), regs);
+  __syncthreads();
+  for (int t0 = 0; t0 < n; t0 += chunk) {
+    const int count = min(chunk, n - t0), next = min(chunk, n - t0 - chunk);
+    const float* buffer = smem + ((t0 / chunk) & 1) * per_buffer;
+    if (next > 0) fetch(t0 + chunk, next, regs);
+    for (int t = 0; t < count; ++t) {
+      const float* row = buffer + t * per_token;
+      const float* q = row + l * kPitch;
+      const float* k = row + vec + l * kPitch;
+      const float v = owner ? row[2 * vec + col] : 0.f;
+      const float beta = row[2 * vec + cols], decay = row[2 * vec + cols + 1];
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPT; e += 4) {
+        const float4 kk = *reinterpret_cast<const float4*>(k + e);
+        S[e] *= decay; S[e + 1] *= decay; S[e + 2] *= decay; S[e + 3] *= decay;
+        a0 = fmaf(S[e], kk.x, a0); a1 = fmaf(S[e + 1], kk.y, a1); a2 = fmaf(S[e + 2], kk.z, a2); a3 = fmaf(S[e + 3], kk.w, a3);
+      }
+      float kv = (a0 + a1) + (a2 + a3);
+      for (int o = lanes >> 1; o > 0; o >>= 1) kv += __shfl_xor_sync(0xffffffffu, kv, o);
+      const float u = beta * (v - kv);
+      a0 = a1 = a2 = a3 = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPT; e += 4) {
+        const float4 kk = *reinterpret_cast<const float4*>(k + e);
+        const float4 qq = *reinterpret_cast<const float4*>(q + e);
+        S[e] = fmaf(kk.x, u, S[e]); S[e + 1] = fmaf(kk.y, u, S[e + 1]);
+        S[e + 2] = fmaf(kk.z, u, S[e + 2]); S[e + 3] = fmaf(kk.w, u, S[e + 3]);
+        a0 = fmaf(S[e], qq.x, a0); a1 = fmaf(S[e + 1], qq.y, a1); a2 = fmaf(S[e + 2], qq.z, a2); a3 = fmaf(S[e + 3], qq.w, a3);
+      }
+      float o = (a0 + a1) + (a2 + a3);
+      for (int w = lanes >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+      if (owner && l == 0) scratch[(int64_t)(t0 + t) * H * V + col] = o;
+    }
+    if (next > 0) stash(smem + (((t0 / chunk) + 1) & 1) * per_buffer, next, regs);
+    __syncthreads();
+  }
+  if (owner) {
+#pragma unroll
+    for (int e = 0; e < EPT; e += 4)
+      *reinterpret_cast<float4*>(mine + (e / 4) * quad_stride) = make_float4(S[e], S[e + 1], S[e + 2], S[e + 3]);
   }
 }
 
-// (elements per lane, lanes per column) for a head of these sizes, or (0, 0) if no form of the kernel takes them
-static void scan_shape(int dim, int v_dim, int& ept, int& lanes) {
-  for (int e : {8, 16, 32, 64, 128}) {
-    int l = 1;
-    while (l * e < dim) l *= 2;
-    const int limit = e <= 32 ? 1024 : (e <= 64 ? 512 : 256);
-    if (l <= 32 && (v_dim * l + 31) / 32 * 32 <= limit) {
-      ept = e;
-      lanes = l;
-      return;
+// The output norm and gate, a warp per (token, head): o / sqrt(mean(o^2) + eps) * w * silu(gate); and, in the warps
+// of head 0, nothing else.  The convolutions' memory moves in a block of its own per sequence (delta_conv_kernel).
+template <typename T>
+__global__ void delta_norm_kernel(DeltaParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int H = p.num_heads, V = p.v_dim;
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= p.num_tokens * H) return;
+  const int64_t token = item / H;
+  const int h = (int)(item - token * H);
+  const int channels = 2 * p.num_kv_heads * p.head_dim + H * V;
+  const int64_t width = (int64_t)channels + (int64_t)H * V + 2 * H;
+  const float* raw = p.scratch + token * H * V + (int64_t)h * V;
+  float ss = 0.f;
+  for (int j = lane; j < V; j += 32) ss += raw[j] * raw[j];
+  const float inv = rsqrtf(warp_sum(ss) / (float)V + p.norm_eps);
+  const T* gate = (const T*)p.x + token * width + channels + (int64_t)h * V;
+  T* dst = (T*)p.out + token * H * V + (int64_t)h * V;
+  for (int j = lane; j < V; j += 32) {
+    const float z = to_float<T>(gate[j]);
+    dst[j] = from_float<T>(raw[j] * inv * p.norm_weight[j] * (z / (1.f + expf(-z))));
+  }
+}
+
+// The convolutions' memory: the last taps - 1 inputs of [what was there before | this step's rows], a block per
+// sequence.
+template <typename T>
+__global__ void delta_conv_kernel(DeltaParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = blockIdx.x;
+  const int64_t first = p.cu_q[s];
+  const int n = (int)(p.cu_q[s + 1] - first);
+  const int slot = p.state_slots[s];
+  if (n <= 0 || slot < 0 || slot >= p.num_slots) return;
+  const int channels = 2 * p.num_kv_heads * p.head_dim + p.num_heads * p.v_dim;
+  const int64_t width = (int64_t)channels + (int64_t)p.num_heads * p.v_dim + 2 * p.num_heads;
+  const T* x = (const T*)p.x;
+  const int keep = p.taps - 1;
+  float* before = p.state + (int64_t)slot * p.state_stride + p.memory;
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    for (int i = 0; i < keep; ++i) {          // ascending: entry i reads entry i + n > i, not yet overwritten
+      const int back = n - keep + i;          // index within the step's tokens of this sequence
+      before[(int64_t)i * channels + c] = back >= 0 ? to_float<T>(x[(first + back) * width + c])
+                                                     : before[(int64_t)(i + n) * channels + c];
     }
   }
-  ept = lanes = 0;
 }
 
-bool delta_scan_supported(int dim, int v_dim) {
-  int ept, lanes;
-  scan_shape(dim, v_dim, ept, lanes);
-  return ept != 0 && dim <= kDeltaMaxDim && v_dim <= kDeltaMaxDim;
-}
-
-template <typename T, int EPT>
-static int launch_scan(const DeltaParams& p, int lanes, cudaStream_t stream) {
-  // at least 128 threads: the fetch of a token's operands is spread over the block (threads without a column idle)
-  const int threads = max(128, (p.v_dim * lanes + 31) / 32 * 32);
-  const size_t smem = 2 * (size_t)ScanLayout<EPT>::floats(lanes, p.v_dim) * sizeof(float);
-  auto kernel = delta_scan_kernel<T, EPT>;
+template <int EPT>
+static int launch_scan(const DeltaParams& p, const ScanShape& shape, cudaStream_t stream) {
+  const int threads = shape.threads;
+  const int per_token = scan_token_floats(shape.lanes, EPT, shape.cols);
+  const size_t smem = 2 * (size_t)shape.chunk * per_token * sizeof(float);
+  auto kernel = delta_scan_kernel<EPT>;
   if (smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
   }
-  return (int)launch_chain(kernel, dim3((unsigned)p.num_seqs, (unsigned)p.num_heads), dim3(threads), smem, stream,
-                           dim3(1, 1, 1), p, lanes);
+  const int splits = (p.v_dim + shape.cols - 1) / shape.cols;
+  return (int)launch_chain(kernel, dim3((unsigned)p.num_seqs, (unsigned)p.num_heads, (unsigned)splits), dim3(threads),
+                           smem, stream, dim3(1, 1, 1), p, shape.lanes, shape.cols, shape.chunk);
 }
 
 int launch_delta_scan(const DeltaParams& p, cudaStream_t stream) {
   if (p.num_tokens == 0 || p.num_seqs == 0) return 0;
-  int ept, lanes;
-  scan_shape(p.head_dim, p.v_dim, ept, lanes);
-  if (ept == 0 || p.head_dim > kDeltaMaxDim || p.v_dim > kDeltaMaxDim || p.num_heads > 65535)
+  const ScanShape shape = scan_shape(p.head_dim, p.v_dim);
+  if (shape.ept == 0 || p.head_dim > kDeltaMaxDim || p.v_dim > kDeltaMaxDim || p.num_heads > 65535 ||
+      p.memory != delta_memory_floats(p.num_heads, p.head_dim, p.v_dim) ||
+      shape.chunk * (2 * p.head_dim + shape.cols + 2) > kScanFetch * shape.threads ||
+      reinterpret_cast<uintptr_t>(p.state) % 16 != 0 || p.state_stride % 4 != 0)      // S moves as float4
     return (int)cudaErrorInvalidValue;
-#define AKV_SCAN(E)                                                                           \
-  case E:                                                                                     \
-    return p.dtype == kBFloat16 ? launch_scan<__nv_bfloat16, E>(p, lanes, stream) : launch_scan<float, E>(p, lanes, stream)
-  switch (ept) {
-    AKV_SCAN(8);
-    AKV_SCAN(16);
-    AKV_SCAN(32);
-    AKV_SCAN(64);
-    AKV_SCAN(128);
+  int err;
+  switch (shape.ept) {
+    case 4: err = launch_scan<4>(p, shape, stream); break;
+    case 8: err = launch_scan<8>(p, shape, stream); break;
+    case 16: err = launch_scan<16>(p, shape, stream); break;
+    default: err = launch_scan<32>(p, shape, stream); break;
   }
-#undef AKV_SCAN
-  return (int)cudaErrorInvalidValue;
+  if (err != 0) return err;
+  const int warps = 4;
+  const int64_t blocks = (p.num_tokens * p.num_heads + warps - 1) / warps;
+  if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  if (p.dtype == kBFloat16)
+    err = (int)launch_chain(delta_norm_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
+                            dim3(1, 1, 1), p);
+  else
+    err = (int)launch_chain(delta_norm_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, dim3(1, 1, 1), p);
+  if (err != 0 || p.taps <= 1) return err;
+  if (p.dtype == kBFloat16)
+    return (int)launch_chain(delta_conv_kernel<__nv_bfloat16>, dim3((unsigned)p.num_seqs), dim3(256), 0, stream,
+                             dim3(1, 1, 1), p);
+  return (int)launch_chain(delta_conv_kernel<float>, dim3((unsigned)p.num_seqs), dim3(256), 0, stream, dim3(1, 1, 1), p);
 }
 
 }  // namespace akv

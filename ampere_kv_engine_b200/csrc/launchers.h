@@ -41,6 +41,12 @@ int launch_add_layernorm(float* hidden, const void* delta, const float* weight, 
 int launch_branch_layernorm(float* hidden, const void* branch, int branch_dtype, const float* weight, void* copy,
                             int copy_dtype, int64_t num_tokens, int64_t hidden_size, float eps, cudaStream_t stream);
 
+// The same with row t of the branch given as the sum of parts[t * top .. t * top + top) (float32 rows) and shared[t]
+// (may be null), added in that order.
+int launch_branch_layernorm_parts(float* hidden, const float* parts, int top, const void* shared, int shared_dtype,
+                                  const float* weight, void* copy, int copy_dtype, int64_t num_tokens,
+                                  int64_t hidden_size, float eps, cudaStream_t stream);
+
 // out (bfloat16) = in (float32), element by element.
 int launch_stream_copy(const float* in, void* out, int64_t total, cudaStream_t stream);
 
@@ -299,7 +305,8 @@ int launch_rotate_pairs(const void* in, void* out, const int32_t* positions, con
 // The gated delta rule (delta_rule.cu).  x [N, q | k | v | gate | beta | step] with num_kv_heads heads of head_dim
 // for q and k, num_heads heads of v_dim for v and gate, one column per head for beta and step.  state
 // [num_slots, state_stride] float32: per slot heads * v_dim * head_dim floats of S ([head][value column][dim]) at
-// offset 0 and (taps - 1) * channels convolution inputs at offset `memory`.
+// offset 0 (in the scan kernel's own order, delta_memory_floats() of them) and (taps - 1) * channels convolution
+// inputs at offset `memory`.
 constexpr int kDeltaMaxDim = 256;
 constexpr int kDeltaMaxTaps = 8;
 struct DeltaParams {
@@ -323,6 +330,7 @@ struct DeltaParams {
 int launch_delta_prep(const DeltaParams& p, cudaStream_t stream);
 int launch_delta_scan(const DeltaParams& p, cudaStream_t stream);
 bool delta_scan_supported(int dim, int v_dim);
+int64_t delta_memory_floats(int num_heads, int dim, int v_dim);
 
 // Routed experts (routed_experts.cu).
 constexpr int kMoeMaxExperts = 512;
@@ -350,8 +358,10 @@ struct MoeGemmParams {
   int experts, k, n, top;
   float limit, slope;
   int dtype;
-  int force_plain;             // 1: the float-arithmetic form even where the tensor-core form takes the sizes
+  int force_plain;             // 0: the form is chosen by size; 1: float arithmetic; 2: mma.sync tiles; 3: few rows
 };
+// steps with at most this many (token, choice) pairs run the few-rows form of the grouped products
+constexpr int kMoeFewRowPairs = 128;
 int launch_moe_gemm(const MoeGemmParams& p, bool gated, cudaStream_t stream);
 // out[t] = sum over c < top of parts[t * top + c] (+ shared[t]), float32.
 int launch_moe_combine(const float* parts, const void* shared, int shared_dtype, float* out, int64_t num_tokens,

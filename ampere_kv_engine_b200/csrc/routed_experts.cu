@@ -479,6 +479,100 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(MoeGemmParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// The same products when an expert has a handful of rows (decode steps): nothing is reused enough to stage, so a
+// warp streams the weight rows of its features straight from global memory in 16-byte pieces and multiplies them
+// with up to four of the expert's rows at a time (their pieces come from L1).  A block per (32 features, expert);
+// an expert without rows costs a look at two integers.  bfloat16, k a multiple of eight.
+namespace {
+constexpr int kGemvRows = 4, kGemvFeatures = 32, kGemvWarps = 8;
+
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+}  // namespace
+
+template <bool GATED>
+__global__ void __launch_bounds__(kGemvWarps * 32) moe_gemv_kernel(MoeGemmParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int expert = blockIdx.y;
+  const int begin = p.offsets[expert], rows = p.offsets[expert + 1] - begin;
+  if (rows <= 0) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int K = p.k, N = p.n, chunks = K / 8;
+  const __nv_bfloat16* a = (const __nv_bfloat16*)p.a;
+  const __nv_bfloat16* w = (const __nv_bfloat16*)p.w + (int64_t)expert * (GATED ? 2 : 1) * N * K;
+  constexpr int kPerWarp = kGemvFeatures / kGemvWarps;
+  for (int r0 = 0; r0 < rows; r0 += kGemvRows) {
+    const int count = min(kGemvRows, rows - r0);
+    const uint4* x[kGemvRows];
+    int pair[kGemvRows];
+#pragma unroll
+    for (int r = 0; r < kGemvRows; ++r) {
+      const int sorted = begin + r0 + min(r, count - 1);        // rows beyond the group repeat its last one, unused
+      pair[r] = p.order[sorted];
+      const int64_t src = GATED ? (int64_t)(pair[r] / p.top) : (int64_t)sorted;
+      x[r] = reinterpret_cast<const uint4*>(a + src * K);
+    }
+    for (int f = 0; f < kPerWarp; ++f) {
+      const int feature = blockIdx.x * kGemvFeatures + warp * kPerWarp + f;
+      if (feature >= N) break;                                    // the same for the whole warp
+      const uint4* wg = reinterpret_cast<const uint4*>(w + (int64_t)feature * K);
+      const uint4* wu = GATED ? reinterpret_cast<const uint4*>(w + (int64_t)(N + feature) * K) : wg;
+      float acc[GATED ? 2 : 1][kGemvRows] = {};
+#pragma unroll 2
+      for (int c = lane; c < chunks; c += 32) {
+        float g[8], u[8];
+        unpack8(wg[c], g);
+        if (GATED) unpack8(wu[c], u);
+#pragma unroll
+        for (int r = 0; r < kGemvRows; ++r) {
+          float v[8];
+          unpack8(x[r][c], v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            acc[0][r] = fmaf(g[i], v[i], acc[0][r]);
+            if (GATED) acc[GATED ? 1 : 0][r] = fmaf(u[i], v[i], acc[GATED ? 1 : 0][r]);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < kGemvRows; ++r) {
+        acc[0][r] = warp_sum(acc[0][r]);
+        if (GATED) acc[GATED ? 1 : 0][r] = warp_sum(acc[GATED ? 1 : 0][r]);
+      }
+      if (lane < count) {
+        float first = 0.f, second = 0.f;
+#pragma unroll
+        for (int r = 0; r < kGemvRows; ++r) {
+          if (r == lane) {
+            first = acc[0][r];
+            second = acc[GATED ? 1 : 0][r];
+          }
+        }
+        if (GATED) {
+          const float g = fminf(first, p.limit);
+          const float u = fminf(fmaxf(second, -p.limit), p.limit);
+          ((__nv_bfloat16*)p.out)[(int64_t)(begin + r0 + lane) * N + feature] =
+              __float2bfloat16_rn(g / (1.f + expf(-p.slope * g)) * (u + 1.f));
+        } else {
+          int mine = pair[0];
+#pragma unroll
+          for (int r = 1; r < kGemvRows; ++r)
+            if (r == lane) mine = pair[r];
+          ((float*)p.out)[(int64_t)mine * N + feature] = p.weights[mine] * first;
+        }
+      }
+    }
+  }
+}
+
 static bool moe_gemm_takes_mma(const MoeGemmParams& p) {
   return p.dtype == kBFloat16 && p.k % 8 == 0 &&
          (reinterpret_cast<uintptr_t>(p.a) | reinterpret_cast<uintptr_t>(p.w)) % 16 == 0;
@@ -487,7 +581,17 @@ static bool moe_gemm_takes_mma(const MoeGemmParams& p) {
 int launch_moe_gemm(const MoeGemmParams& p, bool gated, cudaStream_t stream) {
   if (p.pairs == 0) return 0;
   if (p.experts <= 0 || p.experts > kMoeMaxExperts || p.k <= 0 || p.n <= 0 || p.top <= 0) return (int)cudaErrorInvalidValue;
-  if (moe_gemm_takes_mma(p) && !p.force_plain) {
+  // 0: by size; 1: float arithmetic; 2: mma.sync tiles; 3: the few-rows form
+  const bool tensor_ok = moe_gemm_takes_mma(p);
+  if ((p.force_plain == 2 || p.force_plain == 3) && !tensor_ok) return (int)cudaErrorInvalidValue;
+  if (p.force_plain == 3 || (p.force_plain == 0 && tensor_ok && p.pairs <= kMoeFewRowPairs)) {
+    const int64_t col_tiles = (p.n + kGemvFeatures - 1) / kGemvFeatures;
+    if (col_tiles > 0x7fffffffLL || p.experts > 65535) return (int)cudaErrorInvalidValue;
+    const dim3 grid((unsigned)col_tiles, (unsigned)p.experts);
+    if (gated) return (int)launch_chain(moe_gemv_kernel<true>, grid, dim3(kGemvWarps * 32), 0, stream, dim3(1, 1, 1), p);
+    return (int)launch_chain(moe_gemv_kernel<false>, grid, dim3(kGemvWarps * 32), 0, stream, dim3(1, 1, 1), p);
+  }
+  if (tensor_ok && p.force_plain != 1) {
     const int64_t row_tiles = p.pairs / kMmaRows + (p.pairs < p.experts ? p.pairs : p.experts);
     const int cols = gated ? kMmaWeightRows / 2 : kMmaWeightRows;
     const int64_t col_tiles = (p.n + cols - 1) / cols;

@@ -5,6 +5,8 @@
     python -m ampere_kv_engine_b200.kernels.microbench prefill-attention --tokens 2048
     python -m ampere_kv_engine_b200.kernels.microbench norm --tokens 2048
     python -m ampere_kv_engine_b200.kernels.microbench chain --tokens 8 [--trace]
+    python -m ampere_kv_engine_b200.kernels.microbench delta-scan --tokens 2048 --batch 1 --heads 16 --kv-heads 4
+    python -m ampere_kv_engine_b200.kernels.microbench experts --tokens 2048 --hidden 2048 --intermediate 768
 
 The counterpart of the reference's kernel micro-benchmark (``python -m ampere_kv.paged_decode --benchmark``,
 ampere_kv/paged_decode.py:19-100, CUDA-event windows at 64/256/1024/4096 keys).  Each case cycles through
@@ -249,9 +251,71 @@ def bench_chain(args) -> dict:
     return out
 
 
+def bench_delta_scan(args) -> dict:
+    """The gated delta rule's prep and scan over ``batch`` sequences of ``tokens`` rows each (heads of ``head_dim`` x
+    ``head_dim``, ``kv_heads`` q/k heads, four taps)."""
+    device = torch.device("cuda")
+    H, G, D, taps = args.heads, args.kv_heads, args.head_dim, 4
+    V = D
+    channels = 2 * G * D + H * V
+    n = args.batch * args.tokens
+    g = torch.Generator(device=device).manual_seed(0)
+    x = torch.randn((n, channels + H * V + 2 * H), device=device, generator=g).to(torch.bfloat16)
+    conv = torch.rand((channels, taps), device=device, generator=g) - 0.3
+    rate_log = torch.full((H,), -3.0, device=device)
+    zeros, ones = torch.zeros((H,), device=device), torch.ones((V,), device=device)
+    memory, floats = ops.delta_state_floats(H, G, D, V, taps)
+    copies = copies_for(args.batch * floats * 4) if args.tokens == 1 else 1
+    states = [torch.zeros((args.batch, floats), device=device) for _ in range(copies)]
+    cu = torch.arange(0, n + 1, args.tokens, dtype=torch.int32, device=device)
+    slots = torch.arange(args.batch, dtype=torch.int32, device=device)
+    kw = dict(num_heads=H, num_kv_heads=G, head_dim=D, v_dim=V, taps=taps)
+    qkv, coef = ops.delta_prep(x, conv, rate_log, zeros, states[0], cu, slots, unit_eps=1e-6, **kw)
+    prep_us = timed(lambda i: ops.delta_prep(x, conv, rate_log, zeros, states[i % copies], cu, slots, unit_eps=1e-6, **kw),
+                    args.calls)
+    scan_us = timed(lambda i: ops.delta_scan(qkv, coef, x, ones, states[i % copies], cu, slots, norm_eps=1e-6, **kw),
+                    args.calls)
+    flops = 7.0 * n * H * D * V
+    state_bytes = 2.0 * 4 * args.batch * memory
+    return {"prep_us": prep_us, "scan_norm_conv_us": scan_us, "scan_tflops": flops / scan_us / 1e6,
+            "state_gbs": state_bytes / scan_us / 1e3, "us_per_token_of_a_sequence": scan_us / args.tokens}
+
+
+def bench_experts(args) -> dict:
+    """The routed experts' grouped products for ``tokens`` tokens: ``experts`` experts of ``intermediate`` x
+    ``hidden``, a top of ``top``, random routing."""
+    device = torch.device("cuda")
+    E, top, F, W, n = args.experts, args.top, args.intermediate, args.hidden, args.tokens
+    g = torch.Generator(device=device).manual_seed(0)
+    x = torch.randn((n, W), device=device, generator=g).to(torch.bfloat16)
+    copies = copies_for(E * 3 * F * W * 2) if n * top <= 4 * E else 1
+    w_gu = [(torch.randn((E, 2 * F, W), device=device, generator=g) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    w_d = [(torch.randn((E, W, F), device=device, generator=g) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    logits = torch.randn((n, E), device=device, generator=g)
+    chosen, weights = ops.moe_route(logits, None, top=top, groups=1, keep_groups=1, group_top=2, scale=1.0, weight_eps=1e-20)
+    order, offsets = ops.moe_sort(chosen, E)
+    used = int((offsets[1:] > offsets[:-1]).sum())
+    out = {"experts_with_rows": used}
+    forms = ("few", "mma", "plain") if n * top <= 512 else ("mma",)
+    for form in forms:
+        act = ops.moe_gate_up(x, w_gu[0], order, offsets, top=top, limit=7.0, slope=1.702, kernel=form)
+        up_us = timed(lambda i: ops.moe_gate_up(x, w_gu[i % copies], order, offsets, top=top, limit=7.0, slope=1.702,
+                                                kernel=form), args.calls)
+        down_us = timed(lambda i: ops.moe_down(act, w_d[i % copies], order, offsets, weights, kernel=form), args.calls)
+        out[form] = {"gate_up_us": round(up_us, 2), "down_us": round(down_us, 2),
+                     "gate_up_tflops": round(4.0 * n * top * F * W / up_us / 1e6, 1),
+                     "down_tflops": round(2.0 * n * top * F * W / down_us / 1e6, 1),
+                     "gate_up_weight_gbs": round(2.0 * used * 2 * F * W / up_us / 1e3, 1),
+                     "down_weight_gbs": round(2.0 * used * F * W / down_us / 1e3, 1)}
+    return out
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("kernel", choices=("gemm", "decode-attention", "prefill-attention", "norm", "chain"))
+    parser.add_argument("kernel", choices=("gemm", "decode-attention", "prefill-attention", "norm", "chain",
+                                           "delta-scan", "experts"))
+    parser.add_argument("--experts", type=int, default=32)
+    parser.add_argument("--top", type=int, default=4)
     parser.add_argument("--tokens", type=int, default=8)
     parser.add_argument("--features", type=int, default=24576)
     parser.add_argument("--k", type=int, default=4096)
@@ -278,6 +342,10 @@ def main(argv=None) -> int:
         result = bench_attention(args, 1, args.batch, args.context)
     elif args.kernel == "chain":
         result = bench_chain(args)
+    elif args.kernel == "delta-scan":
+        result = bench_delta_scan(args)
+    elif args.kernel == "experts":
+        result = bench_experts(args)
     elif args.kernel == "prefill-attention":
         result = bench_attention(args, args.tokens, 1, max(args.context, args.tokens) if args.context > args.tokens
                                  else args.tokens)

@@ -101,12 +101,28 @@ class Mirrored:
         self.hidden, self.copy = hidden, copy
 
 
-def branch_layernorm(hidden: torch.Tensor, branch: torch.Tensor, weight: torch.Tensor, eps: float,
+class ExpertParts:
+    """A routed feed-forward's result before its sum: float32 rows ``parts`` [tokens * top, hidden] (a token's
+    ``top`` rows side by side, already weighted) and the shared expert's ``shared`` [tokens, hidden] or None.  A norm
+    that knows it adds them up in the kernel that norms them; anyone else calls :meth:`materialize`."""
+
+    def __init__(self, parts: torch.Tensor, shared: torch.Tensor | None, top: int):
+        self.parts, self.shared, self.top = parts, shared, int(top)
+
+    def materialize(self) -> torch.Tensor:
+        return moe_combine(self.parts, self.shared, top=self.top)
+
+
+def branch_layernorm(hidden: torch.Tensor, branch, weight: torch.Tensor, eps: float,
                      out_dtype: torch.dtype) -> torch.Tensor:
     """``hidden += (branch - mean) / sqrt(var + eps) * weight`` in place, row by row in float32 (``branch`` in the
-    compute dtype or float32).  Returns the new ``hidden`` in ``out_dtype``: a rounded copy, or ``hidden`` itself
-    when ``out_dtype`` is float32."""
+    compute dtype or float32, or an :class:`ExpertParts`).  Returns the new ``hidden`` in ``out_dtype``: a rounded
+    copy, or ``hidden`` itself when ``out_dtype`` is float32."""
     copy = None if out_dtype == torch.float32 else torch.empty(hidden.shape, dtype=out_dtype, device=hidden.device)
+    if isinstance(branch, ExpertParts):
+        ext().branch_layernorm_parts(hidden, branch.parts, branch.shared, weight, copy, float(eps), branch.top)
+        _launched()
+        return hidden if copy is None else copy
     ext().branch_layernorm(hidden, branch, weight, copy, float(eps))
     _launched()
     return hidden if copy is None else copy
@@ -444,18 +460,26 @@ DELTA_MAX_TAPS = 8
 
 def delta_shape(head_dim: int, v_dim: int) -> tuple[int, int] | None:
     """(elements of a value column per lane, lanes per column) of the scan kernel for a head of these sizes, or None
-    when no form of it holds such a head (a block keeps a head's whole memory in registers: at most 1,024 threads of
-    up to 32 elements, 512 of 64 or 256 of 128)."""
+    when it does not take them: the smallest of 4, 8, 16, 32 elements with which at most 8 lanes cover the q/k width."""
     if not (0 < head_dim <= DELTA_MAX_DIM and 0 < v_dim <= DELTA_MAX_VDIM):
         return None
-    for per_lane in (8, 16, 32, 64, 128):
+    for per_lane in (4, 8, 16, 32):
         lanes = 1
         while lanes * per_lane < head_dim:
             lanes *= 2
-        limit = 1024 if per_lane <= 32 else (512 if per_lane <= 64 else 256)
-        if lanes <= 32 and (v_dim * lanes + 31) // 32 * 32 <= limit:
+        if lanes <= 8:
             return per_lane, lanes
     return None
+
+
+def delta_state_floats(num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int, taps: int) -> tuple[int, int]:
+    """(floats of all heads' memory, floats of a request's whole state) as the delta-rule kernels lay a state slot
+    out: every head's memory in the scan kernel's own order (the q/k width padded to lanes times elements per lane),
+    then the last ``taps - 1`` inputs of the convolutions' channels, rounded up to a multiple of four floats."""
+    per_lane, lanes = delta_shape(head_dim, v_dim)
+    memory = num_heads * v_dim * lanes * per_lane
+    channels = 2 * num_kv_heads * head_dim + num_heads * v_dim
+    return memory, (memory + (taps - 1) * channels + 3) // 4 * 4
 
 
 def delta_prep(x, conv, rate_log, step_bias, state, cu_q, state_slots, *, num_heads, num_kv_heads, head_dim, v_dim,
@@ -481,7 +505,7 @@ def delta_prep(x, conv, rate_log, step_bias, state, cu_q, state_slots, *, num_he
 def delta_scan(qkv, coef, x, norm_weight, state, cu_q, state_slots, *, num_heads, num_kv_heads, head_dim, v_dim, taps,
                norm_eps):
     """The recurrence over the step's tokens, sequence by sequence and head by head, from and into ``state``
-    [slots, heads * head_dim * v_dim + (taps - 1) * channels] float32: ``S *= decay; u = beta (v - S^T k);
+    [slots, delta_state_floats(...)[1]] float32: ``S *= decay; u = beta (v - S^T k);
     S += k u^T; o = S^T q``; then ``o / sqrt(mean(o^2) + norm_eps) * norm_weight * silu(gate)`` with the gate columns
     of ``x``.  Also moves the sequence's last ``taps - 1`` convolution inputs (columns of ``x``) into the state.
     Returns [tokens, heads * v_dim] in the dtype of ``x``."""
@@ -489,7 +513,7 @@ def delta_scan(qkv, coef, x, norm_weight, state, cu_q, state_slots, *, num_heads
     scratch = torch.empty((x.shape[0], num_heads * v_dim), dtype=torch.float32, device=x.device)
     ext().delta_scan(qkv, coef, x, norm_weight, state, cu_q, state_slots, scratch, out, num_heads, num_kv_heads,
                      head_dim, v_dim, taps, float(norm_eps))
-    _launched()
+    _launched(3 if taps > 1 else 2)        # the scan, the output norm, the convolutions' memory
     return out
 
 
@@ -497,6 +521,7 @@ def delta_scan(qkv, coef, x, norm_weight, state, cu_q, state_slots, *, num_heads
 
 MOE_MAX_EXPERTS = 512
 MOE_MAX_TOP = 16
+MOE_FORMS = {"auto": 0, "plain": 1, "mma": 2, "few": 3}
 
 
 def moe_route(logits, correction, *, top, groups, keep_groups, group_top, scale, weight_eps):
@@ -527,14 +552,12 @@ def moe_gate_up(x, w_gate_up, order, offsets, *, top, limit, slope, kernel: str 
     """Row r of the result belongs to pair ``order[r]`` and is its expert's ``g * sigmoid(slope * g) * (u + 1)`` with
     ``g = min(W_gate x, limit)``, ``u = clamp(W_up x, -limit, limit)`` for the pair's token;
     ``w_gate_up`` [experts, gate rows then up rows, hidden].  [tokens * top, intermediate] in the dtype of ``x``.
-    ``kernel``: ``"auto"`` takes the tensor cores (mma.sync) for bfloat16 with a hidden size that is a multiple of
-    eight, ``"plain"`` keeps the float-arithmetic form, which is also all of float32."""
+    ``kernel``: ``"auto"``: for bfloat16 with a hidden size that is a multiple of eight, the few-rows form (weights
+    streamed once, no staging) for steps of up to 128 pairs and the tensor cores (``mma.sync`` tiles) above;
+    ``"plain"`` keeps the float-arithmetic form, which is also all of float32; ``"mma"`` / ``"few"`` force one."""
     inter = w_gate_up.shape[1] // 2
     act = torch.empty((order.numel(), inter), dtype=x.dtype, device=x.device)
-    if kernel == "plain":
-        ext().moe_gate_up(x, w_gate_up, order, offsets, act, top, float(limit), float(slope), True)
-    else:
-        ext().moe_gate_up(x, w_gate_up, order, offsets, act, top, float(limit), float(slope))
+    ext().moe_gate_up(x, w_gate_up, order, offsets, act, top, float(limit), float(slope), MOE_FORMS[kernel])
     _launched()
     return act
 
@@ -543,10 +566,7 @@ def moe_down(act, w_down, order, offsets, weights, kernel: str = "auto"):
     """``weights[pair] * W_down[expert] act[r]`` for every sorted row r, written to row ``order[r]`` of a float32
     [tokens * top, hidden].  ``kernel`` as for :func:`moe_gate_up`."""
     out = torch.empty((order.numel(), w_down.shape[1]), dtype=torch.float32, device=act.device)
-    if kernel == "plain":
-        ext().moe_down(act, w_down, order, offsets, weights, out, True)
-    else:
-        ext().moe_down(act, w_down, order, offsets, weights, out)
+    ext().moe_down(act, w_down, order, offsets, weights, out, MOE_FORMS[kernel])
     _launched()
     return out
 

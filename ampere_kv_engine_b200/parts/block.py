@@ -68,5 +68,10 @@ class PostNormBlock(Block):
             x = ops.stream_copy(hidden, self.dtype)
         x = self.mixer_norm.add_normed(hidden, self.mixer.forward(x, ctx, cache), ctx)
         if self.feed_forward is not None:
-            x = self.feed_forward_norm.add_normed(hidden, self.feed_forward.forward(x, ctx), ctx)
+            # a feed-forward whose result is still a sum of rows leaves the sum to a norm that can do it
+            if getattr(self.feed_forward, "defers_sum", False) and getattr(self.feed_forward_norm, "takes_parts", False):
+                branch = self.feed_forward.forward(x, ctx, defer_sum=True)
+            else:
+                branch = self.feed_forward.forward(x, ctx)
+            x = self.feed_forward_norm.add_normed(hidden, branch, ctx)
         return hidden, ops.Mirrored(hidden, x)

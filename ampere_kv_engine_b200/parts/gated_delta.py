@@ -44,8 +44,7 @@ class GatedDelta(Mixer):
             raise ValueError(f"gated_delta: {self.num_heads} heads are not a multiple of {self.num_kv_heads} q/k heads")
         if ops.delta_shape(self.head_dim, self.v_dim) is None:
             raise ValueError(f"gated_delta: q/k width {self.head_dim} with value width {self.v_dim} is outside what "
-                             f"the kernel takes (each up to {ops.DELTA_MAX_DIM}, and a head's memory of "
-                             f"width x value width floats in the registers of one block)")
+                             f"the kernel takes (each up to {ops.DELTA_MAX_DIM})")
         if not 1 <= self.taps <= ops.DELTA_MAX_TAPS:
             raise ValueError(f"gated_delta: {self.taps} taps outside what the kernel takes (1 to {ops.DELTA_MAX_TAPS})")
         self.unit_eps = float(p.get("unit_eps", 1e-6))
@@ -54,11 +53,13 @@ class GatedDelta(Mixer):
         self.qk_width = self.num_kv_heads * self.head_dim
         self.v_width = self.num_heads * self.v_dim
         self.channels = 2 * self.qk_width + self.v_width            # what the convolutions run over
-        self.memory = self.num_heads * self.head_dim * self.v_dim   # floats of S per request
+        # floats of all heads' S per request, and of the whole state with the convolutions' inputs behind it
+        self.memory, self.state_floats = ops.delta_state_floats(self.num_heads, self.num_kv_heads, self.head_dim,
+                                                                self.v_dim, self.taps)
         self.w_in = self.w_o = self.conv = self.rate_log = self.step_bias = self.norm_weight = None
 
     def cache_spec(self) -> CacheSpec:
-        return CacheSpec(kind="none", state_shape=(self.memory + (self.taps - 1) * self.channels,))
+        return CacheSpec(kind="none", state_shape=(self.state_floats,))
 
     def param_specs(self):
         h, n = self.hidden_size, self.names

@@ -63,6 +63,8 @@ class LayerNorm(Norm):
     is added to the stream.  Mean, variance, the scale and the sum are float32."""
 
     graph_safe = True
+    #: ``add_normed`` takes an ``ops.ExpertParts`` as the branch and adds its rows up in the same kernel
+    takes_parts = True
 
     def __init__(self, spec, **kw):
         super().__init__(spec, **kw)

@@ -34,6 +34,8 @@ class RoutedExperts(FeedForward):
     the index, ``gate``, ``up``, ``down``, ``router``, ``correction``, ``shared``)."""
 
     graph_safe = True
+    #: ``forward(..., defer_sum=True)`` hands back an ``ops.ExpertParts`` for a norm that adds the rows up itself
+    defers_sum = True
 
     NAMES = {"expert": "experts.{}", "gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight",
              "router": "router.weight", "correction": "router.correction", "shared": "shared_expert"}
@@ -97,7 +99,7 @@ class RoutedExperts(FeedForward):
                                             dim=0).contiguous()
             self.shared_down = tensors[f"{n['shared']}.{n['down']}"].contiguous()
 
-    def forward(self, x, ctx):
+    def forward(self, x, ctx, defer_sum: bool = False):
         status = getattr(ctx, "status", None)
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32, status=status)
         chosen, weights = ops.moe_route(logits, self.correction, top=self.top, groups=self.groups,
@@ -112,4 +114,5 @@ class RoutedExperts(FeedForward):
             both = ops.linear(x, self.shared_gate_up, status=status)
             shared = ops.linear(ops.glu(both, "clamped_swish", 0, self.shared_limit, self.swish_slope),
                                 self.shared_down, status=status)
-        return ops.moe_combine(parts, shared, top=self.top)
+        result = ops.ExpertParts(parts, shared, self.top)
+        return result if defer_sum else result.materialize()

@@ -673,9 +673,9 @@ def sukalorn_shape(args, design: str = "sukalorn") -> int:
         H, G, D, taps = z["delta_heads"], z["delta_qk_heads"], z["dim"], z["conv"]
         V = D
         channels = 2 * G * D + H * V
-        memory = H * D * V
+        memory, state_floats = ops.delta_state_floats(H, G, D, V, taps)
         g = torch.Generator(device=device).manual_seed(2)
-        state = torch.zeros((batch + 1, memory + (taps - 1) * channels), device=device)
+        state = torch.zeros((batch + 1, state_floats), device=device)
         conv = torch.rand((channels, taps), device=device, generator=g) - 0.3
         rate_log = torch.full((H,), -3.0, device=device)
         zeros_h, ones_v = torch.zeros((H,), device=device), torch.ones((V,), device=device)

@@ -52,6 +52,12 @@ class FakeExt:
         if copy is not None:
             copy.copy_(hidden.to(copy.dtype))
 
+    def branch_layernorm_parts(self, hidden, parts, shared, weight, copy, eps, top):
+        branch = parts.view(-1, top, parts.shape[1]).sum(1)
+        if shared is not None:
+            branch = branch + shared.float()
+        self.branch_layernorm(hidden, branch, weight, copy, eps)
+
     def stream_copy(self, hidden, out):
         out.copy_(hidden.to(out.dtype))
 
@@ -298,9 +304,10 @@ class FakeExt:
 
     def delta_prep(self, x, conv, rate_log, step_bias, state, cu_q, state_slots, qkv, coef, num_heads, num_kv_heads,
                    head_dim, v_dim, taps, unit_eps):
+        from ampere_kv_engine_b200.kernels import ops
         G, D, H, V = num_kv_heads, head_dim, num_heads, v_dim
         channels = 2 * G * D + H * V
-        memory = H * D * V
+        memory = ops.delta_state_floats(H, G, D, V, taps)[0]      # where the convolutions' inputs begin
         cu, slots = cu_q.tolist(), state_slots.tolist()
         xf = x.float()
         qkv.zero_()
@@ -309,7 +316,7 @@ class FakeExt:
             q0, q1 = cu[s], cu[s + 1]
             if slot < 0 or q1 <= q0:
                 continue
-            before = state[slot, memory:].view(taps - 1, channels)
+            before = state[slot, memory:memory + (taps - 1) * channels].view(taps - 1, channels)
             stream = torch.cat((before, xf[q0:q1, :channels]), dim=0)
             y = torch.zeros(q1 - q0, channels)
             for j in range(taps):
@@ -325,16 +332,17 @@ class FakeExt:
 
     def delta_scan(self, qkv, coef, x, norm_weight, state, cu_q, state_slots, scratch, out, num_heads, num_kv_heads,
                    head_dim, v_dim, taps, norm_eps):
+        from ampere_kv_engine_b200.kernels import ops
         G, D, H, V = num_kv_heads, head_dim, num_heads, v_dim
         channels = 2 * G * D + H * V
-        memory = H * D * V
+        memory = ops.delta_state_floats(H, G, D, V, taps)[0]      # the stand-in keeps S in the first H * D * V floats of it
         cu, slots = cu_q.tolist(), state_slots.tolist()
         out.zero_()
         for s, slot in enumerate(slots):
             q0, q1 = cu[s], cu[s + 1]
             if slot < 0 or q1 <= q0:
                 continue
-            S = state[slot, :memory].view(H, D, V).clone()
+            S = state[slot, :H * D * V].view(H, D, V).clone()
             for t in range(q0, q1):
                 q, k = qkv[t, :G * D].view(G, D), qkv[t, G * D:2 * G * D].view(G, D)
                 v = qkv[t, 2 * G * D:].view(H, V)
@@ -347,11 +355,11 @@ class FakeExt:
                     o = S[h].T @ q[j]
                     o = o * torch.rsqrt(o.square().mean() + norm_eps) * norm_weight * (gate[h] * torch.sigmoid(gate[h]))
                     out[t, h * V:(h + 1) * V] = o.to(out.dtype)
-            state[slot, :memory] = S.reshape(-1)
+            state[slot, :H * D * V] = S.reshape(-1)
             if taps > 1:
-                before = state[slot, memory:].view(taps - 1, channels)
+                before = state[slot, memory:memory + (taps - 1) * channels].view(taps - 1, channels)
                 stream = torch.cat((before, x[q0:q1, :channels].float()), dim=0)
-                state[slot, memory:] = stream[-(taps - 1):].reshape(-1)
+                state[slot, memory:memory + (taps - 1) * channels] = stream[-(taps - 1):].reshape(-1)
 
     # ------------------------------------------------------------------ routed experts
 
@@ -380,7 +388,7 @@ class FakeExt:
         offsets[0] = 0
         offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
 
-    def moe_gate_up(self, x, w_gate_up, order, offsets, act, top, limit, slope, plain=False):
+    def moe_gate_up(self, x, w_gate_up, order, offsets, act, top, limit, slope, form=0):
         inter = w_gate_up.shape[1] // 2
         off = offsets.tolist()
         for e in range(len(off) - 1):
@@ -391,7 +399,7 @@ class FakeExt:
             g, u = both[:, :inter].clamp(max=limit), both[:, inter:].clamp(min=-limit, max=limit)
             act[off[e]:off[e + 1]] = (g * torch.sigmoid(slope * g) * (u + 1)).to(act.dtype)
 
-    def moe_down(self, act, w_down, order, offsets, weights, out, plain=False):
+    def moe_down(self, act, w_down, order, offsets, weights, out, form=0):
         off = offsets.tolist()
         flat = weights.reshape(-1)
         for e in range(len(off) - 1):

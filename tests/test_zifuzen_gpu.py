@@ -33,10 +33,10 @@ def _requests(name: str, mixed: bool):
 
 def _check(trace, outputs, expected, dtype):
     """float32: element by element.  bfloat16: every row against its own scale; the stream's rounded copy is what
-    every branch reads, so a row's rounding error is a few per cent of its scale, while a row that is wrong as a
-    whole (a lost state, a wrong page, a wrong expert) misses by its whole scale."""
+    every branch reads and a delta layer's decays and step sizes come from rounded projections, so a row's
+    rounding error is a few per cent of its scale, while a row that is wrong as a whole (a lost state, a wrong page, a wrong expert) misses by its whole scale."""
     if dtype == "bfloat16":
-        return ru.compare_rows_to_scale(trace, outputs, expected, rms_bound=0.05, peak_bound=0.25)
+        return ru.compare_rows_to_scale(trace, outputs, expected, rms_bound=0.1, peak_bound=0.35)
     return ru.compare(trace, outputs, expected, dtype)
 
 

@@ -201,7 +201,7 @@ def test_delta_rule_prompt_portions_and_single_tokens_agree_with_the_plain_recur
     sizes = dict(num_heads=H, num_kv_heads=G, head_dim=D, v_dim=V, taps=taps)
     x, conv, rate_log, step_bias, norm_w = _delta_inputs(H, G, D, V, taps, T, dtype, seed=20)
     want = _delta_plain(x, conv, rate_log, step_bias, norm_w, H, G, D, V, eps)
-    width = H * D * V + (taps - 1) * (2 * G * D + H * V)
+    width = ops.delta_state_floats(H, G, D, V, taps)[1]
     tol = dict(atol=3e-5, rtol=3e-4) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
     results = []
     for cuts, slot in (((T,), 2), ((1,) * T, 0), ((7, 2, 1, 13, 2, 1, 1, 16, 2), 1), ((44, 1), 2)):
@@ -222,7 +222,7 @@ def test_delta_rule_in_a_batch_of_unequal_sequences_with_padding(dtype):
     ops = _ops()
     H, G, D, V, taps, eps = 4, 2, 32, 16, 3, 1e-5
     sizes = dict(num_heads=H, num_kv_heads=G, head_dim=D, v_dim=V, taps=taps)
-    width = H * D * V + (taps - 1) * (2 * G * D + H * V)
+    width = ops.delta_state_floats(H, G, D, V, taps)[1]
     inputs = _delta_inputs(H, G, D, V, taps, 30, dtype, seed=30)
     x, rest = inputs[0], inputs[1:]
     lens, slots = [1, 19, 6, 4], [3, 0, 2, -1]
@@ -264,13 +264,13 @@ def test_delta_rule_keeps_a_key_from_far_back():
     norm_w = torch.ones(V, device="cuda")
     for decay in (1.0, 0.995):
         coef = torch.tensor([[1.0, decay]], device="cuda").repeat(T, 1).contiguous()
-        state = torch.zeros(1, D * V, device="cuda")
-        out = ops.delta_scan(qkv, coef, x, norm_w, state, _i32([0, T]), _i32([0]), norm_eps=0.0 + 1e-12, **sizes)
+        state = torch.zeros(1, ops.delta_state_floats(H, G, D, V, 1)[1], device="cuda")
+        out = ops.delta_scan(qkv, coef, x, norm_w, state, _i32([0, T]), _i32([0]), norm_eps=1e-12, **sizes)
         raw_want = v[5].double() * D ** -0.5 * decay ** (T - 1 - 5)
         want = plain.rms_unit(raw_want, 1e-12) * plain.silu(torch.tensor(4.0, dtype=torch.float64))
         torch.testing.assert_close(out[-1].double(), want.cuda(), atol=1e-4, rtol=1e-4)
     # the same in two steps: the memory carried in the state slot holds the far key
-    state = torch.zeros(2, D * V, device="cuda")
+    state = torch.zeros(2, ops.delta_state_floats(H, G, D, V, 1)[1], device="cuda")
     coef = torch.tensor([[1.0, 1.0]], device="cuda").repeat(T, 1).contiguous()
     ops.delta_scan(qkv[:300].contiguous(), coef[:300].contiguous(), x[:300].contiguous(), norm_w, state, _i32([0, 300]),
                    _i32([1]), norm_eps=1e-12, **sizes)
@@ -293,7 +293,7 @@ def test_convolution_sees_exactly_its_taps_across_a_step_border():
     conv[2 * D + 1] = torch.tensor([0.5, -1.0, 2.0, 1.0])         # last tap: the current token
     zeros = torch.zeros(H, device="cuda")
     for cuts in ((T,), (4, 8), (5, 1, 6), (3, 1, 1, 1, 1, 5)):
-        state = torch.zeros(1, D * V + (taps - 1) * channels, device="cuda")
+        state = torch.zeros(1, ops.delta_state_floats(H, G, D, V, taps)[1], device="cuda")
         got, p = [], 0
         for n in cuts:
             qkv, _ = ops.delta_prep(x[p:p + n].contiguous(), conv, zeros, zeros, state, _i32([0, n]), _i32([0]),
@@ -374,11 +374,14 @@ def test_sort_by_expert():
         assert bool((flat[order[offsets[e]:offsets[e + 1]]] == e).all())
 
 
-@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "auto"), (torch.bfloat16, "auto"), (torch.bfloat16, "plain")])
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "auto"), (torch.bfloat16, "auto"), (torch.bfloat16, "plain"),
+                                          (torch.bfloat16, "mma"), (torch.bfloat16, "few")])
 @pytest.mark.parametrize("tokens,width,inter,experts,top", [(70, 72, 40, 6, 2), (3, 48, 16, 8, 4), (150, 256, 64, 3, 1),
                                                             (1, 100, 33, 5, 2), (200, 136, 200, 2, 2)])
 def test_expert_products_and_sum(dtype, kernel, tokens, width, inter, experts, top):
     ops = _ops()
+    if kernel in ("mma", "few") and width % 8:
+        pytest.skip("the tensor-core and few-rows forms take hidden sizes that are multiples of eight")
     limit, slope = 1.5, 1.702
     x = _randn(tokens, width, seed=70, dtype=dtype)
     w_gu = _randn(experts, 2 * inter, width, seed=71, dtype=dtype, scale=0.3)

@@ -120,7 +120,8 @@ def model_folder(name: str, seed: int = 3) -> str:
             for name_ in ("q", "k", "v"):
                 tensors[f"l{i}.mix.{name_}.conv"] = tensors[f"l{i}.mix.{name_}.conv"] - 0.3     # taps of both signs
         if layer.mlp is not None and layer.mlp.get("kind") == "moe":
-            tensors[f"l{i}.mlp.router"] = tensors[f"l{i}.mlp.router"] * 12.0
+            # router logits of about the same spread at every width
+            tensors[f"l{i}.mlp.router"] = tensors[f"l{i}.mlp.router"] * (12.0 * (72.0 / cfg.width) ** 0.5)
             # expert outputs large enough for the clamps to bite
             for e in range(layer.mlp["router"]["experts"]):
                 tensors[f"l{i}.mlp.e{e}.gate"] = tensors[f"l{i}.mlp.e{e}.gate"] * 15.0
@@ -141,7 +142,7 @@ def plain_logits(folder: str, raw: dict, requests: dict[str, list[int]]) -> dict
     return {rid: plain.forward(raw, w, toks).float() for rid, toks in requests.items()}
 
 
-def decisive_requests(folder: str, raw: dict, lengths, seed: int, margin: float = 0.02, tries: int = 400
+def decisive_requests(folder: str, raw: dict, lengths, seed: int, margin: float = 0.03, tries: int = 400
                       ) -> dict[str, list[int]]:
     """Random requests of the given lengths in which no expert choice is a close call: for every token and routed
     layer the chosen experts (and kept groups) lead the others by at least ``margin`` in the plain implementation, so
