@@ -144,7 +144,9 @@ struct ScanShape {
   int ept, lanes, cols, threads, chunk;   // elements per lane, lanes per column, columns and threads per block, tokens per chunk
 };
 
-constexpr int kScanFetch = 24;      // registers a thread may hold of the chunk under way
+// a thread stages up to kScanRounds entries of each of up to kScanChunk tokens (registers it holds of the chunk
+// under way)
+constexpr int kScanRounds = 3, kScanChunk = 16;
 
 // floats of one staged token in shared memory: q and k (each lane's elements padded by four floats), the block's v
 // columns, beta and decay; a multiple of four, so that every token's q and k can be read as float4
@@ -174,11 +176,12 @@ inline ScanShape scan_shape(int dim, int v_dim) {
   if (s.cols > v_dim) s.cols = v_dim;
   s.threads = (s.cols * s.lanes + 31) / 32 * 32;
   if (s.threads < 128) s.threads = 128;      // the fetch of a chunk is spread over the block (threads without a column idle)
-  // the largest chunk whose two buffers fit in 48 KB and whose fetch fits in the block's registers
+  // a token's entries must fit in kScanRounds rounds of the block
+  while (s.threads * kScanRounds < 2 * dim + s.cols + 2) s.threads += 32;
+  // the largest chunk whose two buffers fit in 48 KB
   const int per_token = scan_token_floats(s.lanes, s.ept, s.cols);
-  s.chunk = 16;
-  while (s.chunk > 1 && (2 * s.chunk * per_token * 4 > 48 * 1024 || s.chunk * (2 * dim + s.cols + 2) > kScanFetch * s.threads))
-    s.chunk /= 2;
+  s.chunk = kScanChunk;
+  while (s.chunk > 1 && 2 * s.chunk * per_token * 4 > 48 * 1024) s.chunk /= 2;
   return s;
 }
 
@@ -193,10 +196,11 @@ int64_t delta_memory_floats(int num_heads, int dim, int v_dim) {
   return (int64_t)num_heads * v_dim * s.lanes * s.ept;
 }
 
-template <int EPT>
-__global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p, int lanes, int cols, int chunk) {
+template <int EPT, int LANES>
+__global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p, int cols, int chunk) {
   extern __shared__ __align__(16) float smem[];
   constexpr int kPitch = EPT + 4;      // a lane's elements of q or k, padded: the lanes of a group read different banks
+  constexpr int lanes = LANES;
   pdl_launch_dependents();
   pdl_wait();
   const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols;
@@ -226,85 +230,105 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p, int lane
     S[e] = v.x; S[e + 1] = v.y; S[e + 2] = v.z; S[e + 3] = v.w;
   }
 
-  const int vec = lanes * kPitch;                        // floats of one token's q (or k) in shared memory
+  constexpr int vec = lanes * kPitch;                                 // floats of one token's q (or k) in shared memory
   const int per_token = scan_token_floats(lanes, EPT, cols);      // q, k, v of the block's columns, beta, decay
   const int per_buffer = chunk * per_token;
+  // What a thread stages of every token: entry i = threadIdx.x + round * blockDim.x of [q | k | v | beta | decay].
+  // Where it comes from (a column of the token's qkv or coef row) and where it goes in the token's shared-memory row
+  // are worked out once; a chunk is then one load per (round, token).
   const int fetch_per_token = 2 * D + mine_cols + 2;
-  // entry idx of a chunk: token idx / fetch_per_token, then [q | k | v | beta | decay]
-  auto fetch = [&](int t0, int count, float (&regs)[kScanFetch]) {
-    const int total = count * fetch_per_token;
+  const float* src[kScanRounds];
+  int src_stride[kScanRounds], dst[kScanRounds];
 #pragma unroll
-    for (int r = 0; r < kScanFetch; ++r) {
-      const int idx = threadIdx.x + r * blockDim.x;
-      float v = 0.f;
-      if (idx < total) {
-        const int t = idx / fetch_per_token, i = idx - t * fetch_per_token;
-        const float* qkv = p.qkv + (first + t0 + t) * channels;
-        const float* coef = p.coef + (first + t0 + t) * 2 * H;
-        if (i < D) v = qkv[g * D + i];
-        else if (i < 2 * D) v = qkv[G * D + g * D + (i - D)];
-        else if (i < 2 * D + mine_cols) v = qkv[2 * G * D + h * V + col0 + (i - 2 * D)];
-        else if (i == 2 * D + mine_cols) v = coef[h];
-        else v = coef[H + h];
+  for (int r = 0; r < kScanRounds; ++r) {
+    const int i = threadIdx.x + r * blockDim.x;
+    src[r] = nullptr;
+    src_stride[r] = 0;
+    dst[r] = 0;
+    if (i < fetch_per_token) {
+      const float* qkv = p.qkv + first * channels;
+      const float* coef = p.coef + first * 2 * H;
+      src_stride[r] = i < 2 * D + mine_cols ? channels : 2 * H;
+      if (i < D) {
+        src[r] = qkv + g * D + i;
+        dst[r] = i / EPT * kPitch + i % EPT;
+      } else if (i < 2 * D) {
+        src[r] = qkv + G * D + g * D + (i - D);
+        dst[r] = vec + (i - D) / EPT * kPitch + (i - D) % EPT;
+      } else if (i < 2 * D + mine_cols) {
+        src[r] = qkv + 2 * G * D + h * V + col0 + (i - 2 * D);
+        dst[r] = 2 * vec + (i - 2 * D);
+      } else {
+        src[r] = coef + (i == 2 * D + mine_cols ? h : H + h);
+        dst[r] = 2 * vec + cols + (i - 2 * D - mine_cols);
       }
-      regs[r] = v;
+    }
+  }
+  float regs[kScanRounds][kScanChunk];
+  auto fetch = [&](int t0, int count) {
+#pragma unroll
+    for (int r = 0; r < kScanRounds; ++r) {
+#pragma unroll
+      for (int t = 0; t < kScanChunk; ++t) {
+        regs[r][t] = 0.f;
+        if (src[r] != nullptr && t < count) regs[r][t] = src[r][(int64_t)(t0 + t) * src_stride[r]];
+      }
     }
   };
-  auto stash = [&](float* buffer, int count, const float (&regs)[kScanFetch]) {
-    const int total = count * fetch_per_token;
+  auto stash = [&](float* buffer, int count) {
 #pragma unroll
-    for (int r = 0; r < kScanFetch; ++r) {
-      const int idx = threadIdx.x + r * blockDim.x;
-      if (idx < total) {
-        const int t = idx / fetch_per_token, i = idx - t * fetch_per_token;
-        float* row = buffer + t * per_token;
-        if (i < D) row[i / EPT * kPitch + i % EPT] = regs[r];
-        else if (i < 2 * D) row[vec + (i - D) / EPT * kPitch + (i - D) % EPT] = regs[r];
-        else row[2 * vec + (i - 2 * D) + (i >= 2 * D + mine_cols ? cols - mine_cols : 0)] = regs[r];
-      }
+    for (int r = 0; r < kScanRounds; ++r) {
+#pragma unroll
+      for (int t = 0; t < kScanChunk; ++t)
+        if (src[r] != nullptr && t < count) buffer[t * per_token + dst[r]] = regs[r][t];
     }
   };
   // elements of q and k beyond the dim stay zero in both buffers
   for (int i = threadIdx.x; i < 2 * per_buffer; i += blockDim.x) smem[i] = 0.f;
   __syncthreads();
-  float regs[kScanFetch];
-  fetch(0, min(chunk, n), regs);
-  stash(smem, min(chunk, n), regs);
+  fetch(0, min(chunk, n));
+  stash(smem, min(chunk, n));
   __syncthreads();
   for (int t0 = 0; t0 < n; t0 += chunk) {
     const int count = min(chunk, n - t0), next = min(chunk, n - t0 - chunk);
     const float* buffer = smem + ((t0 / chunk) & 1) * per_buffer;
-    if (next > 0) fetch(t0 + chunk, next, regs);
-    for (int t = 0; t < count; ++t) {
-      const float* row = buffer + t * per_token;
+    if (next > 0) fetch(t0 + chunk, next);
+    const float* row = buffer;
+    float* o_row = scratch + (int64_t)t0 * H * V + col;
+    // two tokens per round of the loop: the read-out of one token (o = S^T q and its reduction) has no successor in
+    // the chain S -> S^T k -> u -> S and can be issued among the next token's instructions
+#pragma unroll 2
+    for (int t = 0; t < count; ++t, row += per_token, o_row += H * V) {
       const float* q = row + l * kPitch;
       const float* k = row + vec + l * kPitch;
       const float v = owner ? row[2 * vec + col] : 0.f;
       const float beta = row[2 * vec + cols], decay = row[2 * vec + cols + 1];
+      float kr[EPT];
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
       for (int e = 0; e < EPT; e += 4) {
         const float4 kk = *reinterpret_cast<const float4*>(k + e);
-        S[e] *= decay; S[e + 1] *= decay; S[e + 2] *= decay; S[e + 3] *= decay;
+        kr[e] = kk.x; kr[e + 1] = kk.y; kr[e + 2] = kk.z; kr[e + 3] = kk.w;
         a0 = fmaf(S[e], kk.x, a0); a1 = fmaf(S[e + 1], kk.y, a1); a2 = fmaf(S[e + 2], kk.z, a2); a3 = fmaf(S[e + 3], kk.w, a3);
       }
-      float kv = (a0 + a1) + (a2 + a3);
+      float kv = ((a0 + a1) + (a2 + a3)) * decay;           // (decay S)^T k
+#pragma unroll
       for (int o = lanes >> 1; o > 0; o >>= 1) kv += __shfl_xor_sync(0xffffffffu, kv, o);
       const float u = beta * (v - kv);
       a0 = a1 = a2 = a3 = 0.f;
 #pragma unroll
       for (int e = 0; e < EPT; e += 4) {
-        const float4 kk = *reinterpret_cast<const float4*>(k + e);
         const float4 qq = *reinterpret_cast<const float4*>(q + e);
-        S[e] = fmaf(kk.x, u, S[e]); S[e + 1] = fmaf(kk.y, u, S[e + 1]);
-        S[e + 2] = fmaf(kk.z, u, S[e + 2]); S[e + 3] = fmaf(kk.w, u, S[e + 3]);
+        S[e] = fmaf(kr[e], u, S[e] * decay); S[e + 1] = fmaf(kr[e + 1], u, S[e + 1] * decay);
+        S[e + 2] = fmaf(kr[e + 2], u, S[e + 2] * decay); S[e + 3] = fmaf(kr[e + 3], u, S[e + 3] * decay);
         a0 = fmaf(S[e], qq.x, a0); a1 = fmaf(S[e + 1], qq.y, a1); a2 = fmaf(S[e + 2], qq.z, a2); a3 = fmaf(S[e + 3], qq.w, a3);
       }
       float o = (a0 + a1) + (a2 + a3);
+#pragma unroll
       for (int w = lanes >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-      if (owner && l == 0) scratch[(int64_t)(t0 + t) * H * V + col] = o;
+      if (owner && l == 0) *o_row = o;
     }
-    if (next > 0) stash(smem + (((t0 / chunk) + 1) & 1) * per_buffer, next, regs);
+    if (next > 0) stash(smem + (((t0 / chunk) + 1) & 1) * per_buffer, next);
     __syncthreads();
   }
   if (owner) {
@@ -365,35 +389,46 @@ __global__ void delta_conv_kernel(DeltaParams p) {
   }
 }
 
-template <int EPT>
+template <int EPT, int LANES>
 static int launch_scan(const DeltaParams& p, const ScanShape& shape, cudaStream_t stream) {
   const int threads = shape.threads;
   const int per_token = scan_token_floats(shape.lanes, EPT, shape.cols);
   const size_t smem = 2 * (size_t)shape.chunk * per_token * sizeof(float);
-  auto kernel = delta_scan_kernel<EPT>;
+  auto kernel = delta_scan_kernel<EPT, LANES>;
   if (smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
   }
   const int splits = (p.v_dim + shape.cols - 1) / shape.cols;
   return (int)launch_chain(kernel, dim3((unsigned)p.num_seqs, (unsigned)p.num_heads, (unsigned)splits), dim3(threads),
-                           smem, stream, dim3(1, 1, 1), p, shape.lanes, shape.cols, shape.chunk);
+                           smem, stream, dim3(1, 1, 1), p, shape.cols, shape.chunk);
 }
 
 int launch_delta_scan(const DeltaParams& p, cudaStream_t stream) {
   if (p.num_tokens == 0 || p.num_seqs == 0) return 0;
   const ScanShape shape = scan_shape(p.head_dim, p.v_dim);
   if (shape.ept == 0 || p.head_dim > kDeltaMaxDim || p.v_dim > kDeltaMaxDim || p.num_heads > 65535 ||
-      p.memory != delta_memory_floats(p.num_heads, p.head_dim, p.v_dim) ||
-      shape.chunk * (2 * p.head_dim + shape.cols + 2) > kScanFetch * shape.threads ||
+      p.memory != delta_memory_floats(p.num_heads, p.head_dim, p.v_dim) || shape.threads > 256 ||
+      shape.threads * kScanRounds < 2 * p.head_dim + shape.cols + 2 ||
       reinterpret_cast<uintptr_t>(p.state) % 16 != 0 || p.state_stride % 4 != 0)      // S moves as float4
     return (int)cudaErrorInvalidValue;
   int err;
-  switch (shape.ept) {
-    case 4: err = launch_scan<4>(p, shape, stream); break;
-    case 8: err = launch_scan<8>(p, shape, stream); break;
-    case 16: err = launch_scan<16>(p, shape, stream); break;
-    default: err = launch_scan<32>(p, shape, stream); break;
+  // more than four elements per lane only where eight lanes do not cover the dim otherwise
+  if (shape.ept == 4) {
+    switch (shape.lanes) {
+      case 1: err = launch_scan<4, 1>(p, shape, stream); break;
+      case 2: err = launch_scan<4, 2>(p, shape, stream); break;
+      case 4: err = launch_scan<4, 4>(p, shape, stream); break;
+      default: err = launch_scan<4, 8>(p, shape, stream); break;
+    }
+  } else if (shape.lanes != 8) {
+    return (int)cudaErrorInvalidValue;
+  } else if (shape.ept == 8) {
+    err = launch_scan<8, 8>(p, shape, stream);
+  } else if (shape.ept == 16) {
+    err = launch_scan<16, 8>(p, shape, stream);
+  } else {
+    err = launch_scan<32, 8>(p, shape, stream);
   }
   if (err != 0) return err;
   const int warps = 4;

@@ -360,7 +360,8 @@ struct MoeGemmParams {
   int dtype;
   int force_plain;             // 0: the form is chosen by size; 1: float arithmetic; 2: mma.sync tiles; 3: few rows
 };
-// steps with at most this many (token, choice) pairs run the few-rows form of the grouped products
+// steps with at most this many (token, choice) pairs run the few-rows form of the gated product (measured at 8
+// tokens, 64 experts of 1,024 x 4,096: 103 against 111 us; the down product is faster in tiles: 59 against 89 us)
 constexpr int kMoeFewRowPairs = 128;
 int launch_moe_gemm(const MoeGemmParams& p, bool gated, cudaStream_t stream);
 // out[t] = sum over c < top of parts[t * top + c] (+ shared[t]), float32.

@@ -584,7 +584,7 @@ int launch_moe_gemm(const MoeGemmParams& p, bool gated, cudaStream_t stream) {
   // 0: by size; 1: float arithmetic; 2: mma.sync tiles; 3: the few-rows form
   const bool tensor_ok = moe_gemm_takes_mma(p);
   if ((p.force_plain == 2 || p.force_plain == 3) && !tensor_ok) return (int)cudaErrorInvalidValue;
-  if (p.force_plain == 3 || (p.force_plain == 0 && tensor_ok && p.pairs <= kMoeFewRowPairs)) {
+  if (p.force_plain == 3 || (p.force_plain == 0 && tensor_ok && gated && p.pairs <= kMoeFewRowPairs)) {
     const int64_t col_tiles = (p.n + kGemvFeatures - 1) / kGemvFeatures;
     if (col_tiles > 0x7fffffffLL || p.experts > 65535) return (int)cudaErrorInvalidValue;
     const dim3 grid((unsigned)col_tiles, (unsigned)p.experts);

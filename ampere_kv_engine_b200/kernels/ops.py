@@ -553,7 +553,8 @@ def moe_gate_up(x, w_gate_up, order, offsets, *, top, limit, slope, kernel: str 
     ``g = min(W_gate x, limit)``, ``u = clamp(W_up x, -limit, limit)`` for the pair's token;
     ``w_gate_up`` [experts, gate rows then up rows, hidden].  [tokens * top, intermediate] in the dtype of ``x``.
     ``kernel``: ``"auto"``: for bfloat16 with a hidden size that is a multiple of eight, the few-rows form (weights
-    streamed once, no staging) for steps of up to 128 pairs and the tensor cores (``mma.sync`` tiles) above;
+    streamed once, no staging) for the gated product of steps of up to 128 pairs and the tensor cores (``mma.sync``
+    tiles) otherwise;
     ``"plain"`` keeps the float-arithmetic form, which is also all of float32; ``"mma"`` / ``"few"`` force one."""
     inter = w_gate_up.shape[1] // 2
     act = torch.empty((order.numel(), inter), dtype=x.dtype, device=x.device)

@@ -419,9 +419,11 @@ def test_expert_products_and_sum(dtype, kernel, tokens, width, inter, experts, t
                                **(tol if dtype == torch.float32 else dict(atol=8e-2, rtol=3e-2)))
 
 
-def test_a_row_of_the_expert_products_does_not_depend_on_the_rest_of_the_batch():
-    """The same token alone and among 99 others: bit-equal results (its dot products are accumulated in one order
-    whatever tile it falls in)."""
+@pytest.mark.parametrize("kernel", ["mma", "few", "plain"])
+def test_a_row_of_the_expert_products_does_not_depend_on_the_rest_of_the_batch(kernel):
+    """The same token alone and among 99 others: bit-equal results within each form of the products (its dot products
+    are accumulated in one order whatever tile or row group it falls in), and equal up to the order of the sums
+    between the forms, which the size of a step chooses."""
     ops = _ops()
     width, inter, experts, top = 96, 48, 4, 2
     x = _randn(100, width, seed=80, dtype=torch.bfloat16)
@@ -431,11 +433,14 @@ def test_a_row_of_the_expert_products_does_not_depend_on_the_rest_of_the_batch()
                          ).to(torch.int32)
     weights = torch.rand(100, top, generator=_gen(84), device="cuda")
 
-    def run(rows):
+    def run(rows, form):
         order, offsets = ops.moe_sort(chosen[rows].contiguous(), experts)
-        act = ops.moe_gate_up(x[rows].contiguous(), w_gu, order, offsets, top=top, limit=2.0, slope=1.702)
-        return ops.moe_combine(ops.moe_down(act, w_d, order, offsets, weights[rows].contiguous()), None, top=top)
+        act = ops.moe_gate_up(x[rows].contiguous(), w_gu, order, offsets, top=top, limit=2.0, slope=1.702, kernel=form)
+        return ops.moe_combine(ops.moe_down(act, w_d, order, offsets, weights[rows].contiguous(), kernel=form), None,
+                               top=top)
 
-    everyone = run(slice(0, 100))
+    everyone = run(slice(0, 100), kernel)
+    by_size = run(slice(0, 100), "auto")
     for t in (0, 37, 99):
-        torch.testing.assert_close(run(slice(t, t + 1))[0], everyone[t], atol=0, rtol=0)
+        torch.testing.assert_close(run(slice(t, t + 1), kernel)[0], everyone[t], atol=0, rtol=0)
+        torch.testing.assert_close(run(slice(t, t + 1), "auto")[0], by_size[t], atol=2e-6, rtol=2e-5)
