@@ -1198,6 +1198,19 @@ void moe_route(const Tensor& logits, const OptTensor& correction, Tensor& chosen
   check_launch(akv::launch_moe_route(p, stream_of(logits)), "moe_route");
 }
 
+void moe_router(const Tensor& x, const Tensor& w, Tensor& logits) {
+  check_cuda(x, "x");
+  check_cuda(w, "w");
+  check_same(x, w, "x", "w");
+  AKV_CHECK(x.dim() == 2 && w.dim() == 2 && w.size(1) == x.size(1), "moe_router: x [tokens, hidden], w [experts, hidden]");
+  check_f32(logits, "logits", x.size(0) * w.size(0));
+  AKV_CHECK(x.size(0) <= 65535, "moe_router: at most 65535 tokens");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(akv::launch_moe_router(x.data_ptr(), w.data_ptr(), logits.data_ptr<float>(), x.size(0), (int)w.size(0),
+                                      (int)x.size(1), dtype_code(x, "x"), stream_of(x)),
+               "moe_router");
+}
+
 void moe_sort(const Tensor& chosen, Tensor& order, Tensor& offsets) {
   check_i32(chosen, "chosen");
   check_i32(order, "order", chosen.numel());
@@ -1401,6 +1414,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("moe_route", &moe_route, py::arg("logits"), py::arg("correction"), py::arg("chosen"), py::arg("weights"),
         py::arg("groups"), py::arg("keep_groups"), py::arg("group_top"), py::arg("scale"), py::arg("weight_eps"));
+  m.def("moe_router", &moe_router, py::arg("x"), py::arg("w"), py::arg("logits"));
   m.def("moe_sort", &moe_sort, py::arg("chosen"), py::arg("order"), py::arg("offsets"));
   m.def("moe_gate_up", &moe_gate_up, py::arg("x"), py::arg("w"), py::arg("order"), py::arg("offsets"), py::arg("act"),
         py::arg("top"), py::arg("limit"), py::arg("slope"), py::arg("form") = 0);

@@ -10,8 +10,8 @@
 //                A thread group of up to 8 lanes owns one value column of S (in registers for the whole step); the
 //                two products are a few multiply-adds per lane and a shuffle reduction over the group; tokens are
 //                staged through shared memory in chunks, so a token costs no block barrier.  A second kernel applies
-//                the output norm o / sqrt(mean(o^2) + eps) * w * silu(gate) to all tokens in parallel, a third moves
-//                each sequence's last taps - 1 convolution inputs into the state.
+//                the output norm o / sqrt(mean(o^2) + eps) * w * silu(gate) to all tokens in parallel and, in further
+//                blocks, moves each sequence's last taps - 1 convolution inputs into the state.
 //
 // The walk is token by token whatever the step holds, so the state after a token does not depend on how the
 // tokens were cut into steps.  A sequence whose state slot is negative (padding of a captured step) is left alone
@@ -338,55 +338,57 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p, int cols
   }
 }
 
-// The output norm and gate, a warp per (token, head): o / sqrt(mean(o^2) + eps) * w * silu(gate); and, in the warps
-// of head 0, nothing else.  The convolutions' memory moves in a block of its own per sequence (delta_conv_kernel).
+// What follows the scan, in one launch.  Blocks [0, norm_blocks): the output norm and gate, a warp per (token, head):
+// o / sqrt(mean(o^2) + eps) * w * silu(gate).  The blocks after them: the convolutions' memory, a thread per
+// (sequence, channel): the last taps - 1 inputs of [what was there before | this step's rows]; a thread reads all it
+// needs before it writes.
 template <typename T>
-__global__ void delta_norm_kernel(DeltaParams p) {
+__global__ void __launch_bounds__(128) delta_finish_kernel(DeltaParams p, int norm_blocks, int channel_blocks) {
   pdl_launch_dependents();
   pdl_wait();
-  const int lane = threadIdx.x & 31;
   const int H = p.num_heads, V = p.v_dim;
-  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (item >= p.num_tokens * H) return;
-  const int64_t token = item / H;
-  const int h = (int)(item - token * H);
   const int channels = 2 * p.num_kv_heads * p.head_dim + H * V;
   const int64_t width = (int64_t)channels + (int64_t)H * V + 2 * H;
-  const float* raw = p.scratch + token * H * V + (int64_t)h * V;
-  float ss = 0.f;
-  for (int j = lane; j < V; j += 32) ss += raw[j] * raw[j];
-  const float inv = rsqrtf(warp_sum(ss) / (float)V + p.norm_eps);
-  const T* gate = (const T*)p.x + token * width + channels + (int64_t)h * V;
-  T* dst = (T*)p.out + token * H * V + (int64_t)h * V;
-  for (int j = lane; j < V; j += 32) {
-    const float z = to_float<T>(gate[j]);
-    dst[j] = from_float<T>(raw[j] * inv * p.norm_weight[j] * (z / (1.f + expf(-z))));
+  const T* x = (const T*)p.x;
+  if ((int)blockIdx.x < norm_blocks) {
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= p.num_tokens * H) return;
+    const int64_t token = item / H;
+    const int h = (int)(item - token * H);
+    const float* raw = p.scratch + token * H * V + (int64_t)h * V;
+    float ss = 0.f;
+    for (int j = lane; j < V; j += 32) ss += raw[j] * raw[j];
+    const float inv = rsqrtf(warp_sum(ss) / (float)V + p.norm_eps);
+    const T* gate = x + token * width + channels + (int64_t)h * V;
+    T* dst = (T*)p.out + token * H * V + (int64_t)h * V;
+    for (int j = lane; j < V; j += 32) {
+      const float z = to_float<T>(gate[j]);
+      dst[j] = from_float<T>(raw[j] * inv * p.norm_weight[j] * (z / (1.f + expf(-z))));
+    }
+    return;
   }
-}
-
-// The convolutions' memory: the last taps - 1 inputs of [what was there before | this step's rows], a block per
-// sequence.
-template <typename T>
-__global__ void delta_conv_kernel(DeltaParams p) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int s = blockIdx.x;
+  const int block = (int)blockIdx.x - norm_blocks;
+  const int s = block / channel_blocks;
+  const int c = (block - s * channel_blocks) * blockDim.x + threadIdx.x;
   const int64_t first = p.cu_q[s];
   const int n = (int)(p.cu_q[s + 1] - first);
   const int slot = p.state_slots[s];
-  if (n <= 0 || slot < 0 || slot >= p.num_slots) return;
-  const int channels = 2 * p.num_kv_heads * p.head_dim + p.num_heads * p.v_dim;
-  const int64_t width = (int64_t)channels + (int64_t)p.num_heads * p.v_dim + 2 * p.num_heads;
-  const T* x = (const T*)p.x;
+  if (c >= channels || n <= 0 || slot < 0 || slot >= p.num_slots) return;
   const int keep = p.taps - 1;
   float* before = p.state + (int64_t)slot * p.state_stride + p.memory;
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-    for (int i = 0; i < keep; ++i) {          // ascending: entry i reads entry i + n > i, not yet overwritten
+  float kept[kDeltaMaxTaps - 1];
+#pragma unroll
+  for (int i = 0; i < kDeltaMaxTaps - 1; ++i) {
+    kept[i] = 0.f;
+    if (i < keep) {
       const int back = n - keep + i;          // index within the step's tokens of this sequence
-      before[(int64_t)i * channels + c] = back >= 0 ? to_float<T>(x[(first + back) * width + c])
-                                                     : before[(int64_t)(i + n) * channels + c];
+      kept[i] = back >= 0 ? to_float<T>(x[(first + back) * width + c]) : before[(int64_t)(i + n) * channels + c];
     }
   }
+#pragma unroll
+  for (int i = 0; i < kDeltaMaxTaps - 1; ++i)
+    if (i < keep) before[(int64_t)i * channels + c] = kept[i];
 }
 
 template <int EPT, int LANES>
@@ -432,18 +434,16 @@ int launch_delta_scan(const DeltaParams& p, cudaStream_t stream) {
   }
   if (err != 0) return err;
   const int warps = 4;
-  const int64_t blocks = (p.num_tokens * p.num_heads + warps - 1) / warps;
+  const int64_t norm_blocks = (p.num_tokens * p.num_heads + warps - 1) / warps;
+  const int channels = 2 * p.num_kv_heads * p.head_dim + p.num_heads * p.v_dim;
+  const int channel_blocks = p.taps > 1 ? (channels + warps * 32 - 1) / (warps * 32) : 0;
+  const int64_t blocks = norm_blocks + (int64_t)p.num_seqs * channel_blocks;
   if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
   if (p.dtype == kBFloat16)
-    err = (int)launch_chain(delta_norm_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
-                            dim3(1, 1, 1), p);
-  else
-    err = (int)launch_chain(delta_norm_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, dim3(1, 1, 1), p);
-  if (err != 0 || p.taps <= 1) return err;
-  if (p.dtype == kBFloat16)
-    return (int)launch_chain(delta_conv_kernel<__nv_bfloat16>, dim3((unsigned)p.num_seqs), dim3(256), 0, stream,
-                             dim3(1, 1, 1), p);
-  return (int)launch_chain(delta_conv_kernel<float>, dim3((unsigned)p.num_seqs), dim3(256), 0, stream, dim3(1, 1, 1), p);
+    return (int)launch_chain(delta_finish_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
+                             dim3(1, 1, 1), p, (int)norm_blocks, channel_blocks);
+  return (int)launch_chain(delta_finish_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, dim3(1, 1, 1),
+                           p, (int)norm_blocks, channel_blocks);
 }
 
 }  // namespace akv

@@ -344,6 +344,9 @@ struct MoeRouteParams {
   float scale, weight_eps;
 };
 int launch_moe_route(const MoeRouteParams& p, cudaStream_t stream);
+// logits[t, e] = x[t, :] . w[e, :] in float, a warp per (token, expert): for steps of a few tokens.
+int launch_moe_router(const void* x, const void* w, float* logits, int64_t tokens, int experts, int k, int dtype,
+                      cudaStream_t stream);
 // order [pairs]: the (token, choice) pairs (token * top + choice) sorted by expert; offsets [experts + 1].
 int launch_moe_sort(const int32_t* chosen, int32_t* order, int32_t* offsets, int64_t pairs, int experts,
                     cudaStream_t stream);

@@ -1,5 +1,6 @@
 // A feed-forward of routed experts, entirely on the device (no host read of the routing).
 //
+//   moe_router:   the router's logits for a few tokens (a warp per token and expert); larger steps use the library.
 //   moe_route:    per token: s = sigmoid(logits); choice = s + correction; the experts form equal groups of
 //                 neighbours, a group's score is the sum of its group_top largest choice scores, only experts of the
 //                 keep best groups can be chosen; the top largest remaining choice scores are chosen (ties: the lower
@@ -128,6 +129,58 @@ __global__ void moe_route_kernel(MoeRouteParams p) {
     p.chosen[token * p.top + lane] = my_expert;
     p.weights[token * p.top + lane] = my_score / (picked_sum + p.weight_eps) * p.scale;
   }
+}
+
+// Router logits of a few tokens: a warp per (token, expert), the dot product over the hidden size in float.  (The
+// library's product of a handful of rows with a matrix of a few dozen rows runs on one or two SMs.)
+template <typename T>
+__global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                         float* __restrict__ logits, int experts, int k) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int expert = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t token = blockIdx.y;
+  if (expert >= experts) return;
+  const T* a = x + token * k;
+  const T* b = w + (int64_t)expert * k;
+  float sum = 0.f;
+  constexpr int kVec = 16 / sizeof(T);
+  if (k % kVec == 0 && (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) % 16 == 0) {
+    float s0 = 0.f, s1 = 0.f;
+    for (int c = lane * kVec; c < k; c += 32 * kVec) {
+      if constexpr (sizeof(T) == 2) {
+        float u[8], v[8];
+        load8<T>(a + c, u);
+        load8<T>(b + c, v);
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          s0 = fmaf(u[i], v[i], s0);
+          s1 = fmaf(u[i + 1], v[i + 1], s1);
+        }
+      } else {
+        const float4 u = *reinterpret_cast<const float4*>(a + c), v = *reinterpret_cast<const float4*>(b + c);
+        s0 = fmaf(u.x, v.x, s0); s1 = fmaf(u.y, v.y, s1); s0 = fmaf(u.z, v.z, s0); s1 = fmaf(u.w, v.w, s1);
+      }
+    }
+    sum = s0 + s1;
+  } else {
+    for (int c = lane; c < k; c += 32) sum = fmaf(to_float<T>(a[c]), to_float<T>(b[c]), sum);
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) logits[token * experts + expert] = sum;
+}
+
+int launch_moe_router(const void* x, const void* w, float* logits, int64_t tokens, int experts, int k, int dtype,
+                      cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (experts <= 0 || k <= 0 || tokens > 65535) return (int)cudaErrorInvalidValue;
+  const dim3 grid((unsigned)((experts + 7) / 8), (unsigned)tokens);
+  if (dtype == kBFloat16)
+    return (int)launch_chain(moe_router_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, dim3(1, 1, 1),
+                             (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, logits, experts, k);
+  return (int)launch_chain(moe_router_kernel<float>, grid, dim3(256), 0, stream, dim3(1, 1, 1), (const float*)x,
+                           (const float*)w, logits, experts, k);
 }
 
 int launch_moe_route(const MoeRouteParams& p, cudaStream_t stream) {

@@ -513,7 +513,7 @@ def delta_scan(qkv, coef, x, norm_weight, state, cu_q, state_slots, *, num_heads
     scratch = torch.empty((x.shape[0], num_heads * v_dim), dtype=torch.float32, device=x.device)
     ext().delta_scan(qkv, coef, x, norm_weight, state, cu_q, state_slots, scratch, out, num_heads, num_kv_heads,
                      head_dim, v_dim, taps, float(norm_eps))
-    _launched(3 if taps > 1 else 2)        # the scan, the output norm, the convolutions' memory
+    _launched(2)        # the scan; the output norm and the convolutions' memory
     return out
 
 
@@ -522,6 +522,21 @@ def delta_scan(qkv, coef, x, norm_weight, state, cu_q, state_slots, *, num_heads
 MOE_MAX_EXPERTS = 512
 MOE_MAX_TOP = 16
 MOE_FORMS = {"auto": 0, "plain": 1, "mma": 2, "few": 3}
+
+
+#: steps of at most this many tokens compute the router's logits with a warp per (token, expert); the library's
+#: product of so few rows with a matrix of a few dozen rows runs on one or two SMs
+MOE_ROUTER_TOKENS = 64
+
+
+def moe_router_logits(x, w_router, status=None):
+    """float32 ``x @ w_router.T`` [tokens, experts], accumulated in float32 whatever the operands' dtype."""
+    if x.shape[0] <= MOE_ROUTER_TOKENS:
+        logits = torch.empty((x.shape[0], w_router.shape[0]), dtype=torch.float32, device=x.device)
+        ext().moe_router(x, w_router, logits)
+        _launched()
+        return logits
+    return linear(x, w_router, out_dtype=torch.float32, status=status)
 
 
 def moe_route(logits, correction, *, top, groups, keep_groups, group_top, scale, weight_eps):

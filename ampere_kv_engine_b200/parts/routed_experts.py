@@ -11,7 +11,7 @@
     y       = sum_e w_e expert_e(x)  +  shared(x)
 
 Everything runs on the device from the batch layout alone (no host read of the routing), so a decode step through it
-can be replayed as a CUDA graph: the router's product, one kernel that scores and chooses (``ops.moe_route``), a
+can be replayed as a CUDA graph: the router's product (``ops.moe_router_logits``), one kernel that scores and chooses (``ops.moe_route``), a
 counting sort of the (token, choice) pairs by expert (``ops.moe_sort``), two grouped products over the sorted rows
 (``ops.moe_gate_up`` with the activation on its output, ``ops.moe_down`` with the token's weight), and a sum in a
 fixed order (``ops.moe_combine``).  The experts' matrices are stacked [experts, rows, columns] at load.
@@ -101,7 +101,7 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x, ctx, defer_sum: bool = False):
         status = getattr(ctx, "status", None)
-        logits = ops.linear(x, self.w_router, out_dtype=torch.float32, status=status)
+        logits = ops.moe_router_logits(x, self.w_router, status=status)
         chosen, weights = ops.moe_route(logits, self.correction, top=self.top, groups=self.groups,
                                         keep_groups=self.keep_groups, group_top=self.group_top,
                                         scale=self.route_scale, weight_eps=self.weight_eps)

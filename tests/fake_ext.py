@@ -381,6 +381,9 @@ class FakeExt:
         chosen.copy_(ids.to(torch.int32))
         weights.copy_(picked / (picked.sum(-1, keepdim=True) + weight_eps) * scale)
 
+    def moe_router(self, x, w, logits):
+        logits.copy_(x.float() @ w.float().T)
+
     def moe_sort(self, chosen, order, offsets):
         flat = chosen.reshape(-1).long()
         order.copy_(torch.sort(flat, stable=True).indices.to(torch.int32))

@@ -330,6 +330,16 @@ def test_route_follows_the_plain_router(experts, top, groups, keep):
     torch.testing.assert_close(weights.double().cpu(), want_w, atol=1e-6, rtol=1e-5)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens,experts,width", [(1, 12, 256), (8, 64, 1000), (64, 5, 72), (3, 7, 33), (70, 6, 48)])
+def test_router_logits(dtype, tokens, experts, width):
+    ops = _ops()
+    x, w = _randn(tokens, width, seed=55, dtype=dtype), _randn(experts, width, seed=56, dtype=dtype)
+    got = ops.moe_router_logits(x, w)
+    assert got.dtype == torch.float32
+    torch.testing.assert_close(got.double(), x.double() @ w.double().T, atol=2e-4, rtol=1e-5)
+
+
 def test_route_engineered_cases():
     ops = _ops()
     kw = dict(group_top=2, scale=1.0, weight_eps=1e-20)
