@@ -178,10 +178,11 @@ inline ScanShape scan_shape(int dim, int v_dim) {
   if (s.threads < 128) s.threads = 128;      // the fetch of a chunk is spread over the block (threads without a column idle)
   // a token's entries must fit in kScanRounds rounds of the block
   while (s.threads * kScanRounds < 2 * dim + s.cols + 2) s.threads += 32;
-  // the largest chunk whose two buffers fit in 48 KB
+  // the chunk of a prompt: 16 tokens, 8 where a lane holds 32 elements (two buffers within 48 KB)
   const int per_token = scan_token_floats(s.lanes, s.ept, s.cols);
   s.chunk = kScanChunk;
   while (s.chunk > 1 && 2 * s.chunk * per_token * 4 > 48 * 1024) s.chunk /= 2;
+  if (s.ept >= 32 && s.chunk > 8) s.chunk = 8;
   return s;
 }
 
@@ -196,8 +197,9 @@ int64_t delta_memory_floats(int num_heads, int dim, int v_dim) {
   return (int64_t)num_heads * v_dim * s.lanes * s.ept;
 }
 
-template <int EPT, int LANES>
-__global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p, int cols, int chunk) {
+template <int EPT, int LANES, int CHUNK>
+__global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p, int cols) {
+  constexpr int chunk = CHUNK;
   extern __shared__ __align__(16) float smem[];
   constexpr int kPitch = EPT + 4;      // a lane's elements of q or k, padded: the lanes of a group read different banks
   constexpr int lanes = LANES;
@@ -264,12 +266,12 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p, int cols
       }
     }
   }
-  float regs[kScanRounds][kScanChunk];
+  float regs[kScanRounds][CHUNK];
   auto fetch = [&](int t0, int count) {
 #pragma unroll
     for (int r = 0; r < kScanRounds; ++r) {
 #pragma unroll
-      for (int t = 0; t < kScanChunk; ++t) {
+      for (int t = 0; t < CHUNK; ++t) {
         regs[r][t] = 0.f;
         if (src[r] != nullptr && t < count) regs[r][t] = src[r][(int64_t)(t0 + t) * src_stride[r]];
       }
@@ -279,7 +281,7 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaParams p, int cols
 #pragma unroll
     for (int r = 0; r < kScanRounds; ++r) {
 #pragma unroll
-      for (int t = 0; t < kScanChunk; ++t)
+      for (int t = 0; t < CHUNK; ++t)
         if (src[r] != nullptr && t < count) buffer[t * per_token + dst[r]] = regs[r][t];
     }
   };
@@ -391,19 +393,29 @@ __global__ void __launch_bounds__(128) delta_finish_kernel(DeltaParams p, int no
     if (i < keep) before[(int64_t)i * channels + c] = kept[i];
 }
 
-template <int EPT, int LANES>
-static int launch_scan(const DeltaParams& p, const ScanShape& shape, cudaStream_t stream) {
+template <int EPT, int LANES, int CHUNK>
+static int launch_scan_chunk(const DeltaParams& p, const ScanShape& shape, cudaStream_t stream) {
   const int threads = shape.threads;
   const int per_token = scan_token_floats(shape.lanes, EPT, shape.cols);
-  const size_t smem = 2 * (size_t)shape.chunk * per_token * sizeof(float);
-  auto kernel = delta_scan_kernel<EPT, LANES>;
+  const size_t smem = 2 * (size_t)CHUNK * per_token * sizeof(float);
+  auto kernel = delta_scan_kernel<EPT, LANES, CHUNK>;
   if (smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
   }
   const int splits = (p.v_dim + shape.cols - 1) / shape.cols;
   return (int)launch_chain(kernel, dim3((unsigned)p.num_seqs, (unsigned)p.num_heads, (unsigned)splits), dim3(threads),
-                           smem, stream, dim3(1, 1, 1), p, shape.cols, shape.chunk);
+                           smem, stream, dim3(1, 1, 1), p, shape.cols);
+}
+
+// Steps of about a token per sequence (decoding) stage two tokens at a time: fewer registers and less shared memory
+// per block, so more blocks share an SM while the state streams through; prompts stage the largest chunk that fits.
+template <int EPT, int LANES>
+static int launch_scan(const DeltaParams& p, const ScanShape& shape, cudaStream_t stream) {
+  constexpr int kLong = EPT >= 32 ? 8 : 16;
+  if (p.num_tokens <= 2 * (int64_t)p.num_seqs) return launch_scan_chunk<EPT, LANES, 2>(p, shape, stream);
+  if (shape.chunk < kLong) return (int)cudaErrorInvalidValue;
+  return launch_scan_chunk<EPT, LANES, kLong>(p, shape, stream);
 }
 
 int launch_delta_scan(const DeltaParams& p, cudaStream_t stream) {

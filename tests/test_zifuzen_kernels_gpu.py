@@ -216,27 +216,32 @@ def test_delta_rule_prompt_portions_and_single_tokens_agree_with_the_plain_recur
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_delta_rule_in_a_batch_of_unequal_sequences_with_padding(dtype):
-    """Three sequences of 1, 19 and 6 rows and a padded one share a step; each result equals the sequence alone, the
-    padded sequence's rows are zero and no slot but the three is written."""
+@pytest.mark.parametrize("lens", [[1, 19, 6, 4], [1, 5, 1, 1], [2, 3, 1, 2]])
+def test_delta_rule_in_a_batch_of_unequal_sequences_with_padding(dtype, lens):
+    """Three sequences (of 1, 19 and 6 rows; or of so few rows that the step counts as decoding and is staged two
+    tokens at a time) and a padded one share a step; each result equals the sequence alone, the padded sequence's rows
+    are zero and no slot but the three is written."""
     ops = _ops()
     H, G, D, V, taps, eps = 4, 2, 32, 16, 3, 1e-5
     sizes = dict(num_heads=H, num_kv_heads=G, head_dim=D, v_dim=V, taps=taps)
     width = ops.delta_state_floats(H, G, D, V, taps)[1]
     inputs = _delta_inputs(H, G, D, V, taps, 30, dtype, seed=30)
     x, rest = inputs[0], inputs[1:]
-    lens, slots = [1, 19, 6, 4], [3, 0, 2, -1]
+    slots = [3, 0, 2, -1]
     state = torch.zeros(5, width, device="cuda")
     state[1] = 5.0
     state[4] = -3.0
-    cu = [0, 1, 20, 26, 30]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    x = x[:cu[-1]].contiguous()
     qkv, coef = ops.delta_prep(x, rest[0], rest[1], rest[2], state, _i32(cu), _i32(slots), unit_eps=1e-6, **sizes)
     out = ops.delta_scan(qkv, coef, x, rest[3], state, _i32(cu), _i32(slots), norm_eps=eps, **sizes)
     tol = dict(atol=3e-5, rtol=3e-4) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
     for i in range(3):
         want = _delta_plain(x[cu[i]:cu[i + 1]], *rest, H, G, D, V, eps)
         torch.testing.assert_close(out[cu[i]:cu[i + 1]].double().cpu(), want, **tol)
-    assert float(out[26:].float().abs().max()) == 0.0
+    assert float(out[cu[3]:].float().abs().max()) == 0.0
     assert bool((state[1] == 5.0).all()) and bool((state[4] == -3.0).all())
 
 
