@@ -308,7 +308,7 @@ int launch_rotate_pairs(const void* in, void* out, const int32_t* positions, con
 // offset 0 (in the scan kernel's own order, delta_memory_floats() of them) and (taps - 1) * channels convolution
 // inputs at offset `memory`.
 constexpr int kDeltaMaxDim = 256;
-constexpr int kDeltaMaxTaps = 8;
+constexpr int kDeltaMaxTaps = 16;
 struct DeltaParams {
   const void* x;
   const float* conv;           // [channels, taps], channels = 2 * num_kv_heads * head_dim + num_heads * v_dim

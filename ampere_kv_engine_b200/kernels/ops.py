@@ -455,7 +455,7 @@ def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
 #: what the delta-rule kernels take: q/k width, value width (a block holds a value column per thread group), taps
 DELTA_MAX_DIM = 256
 DELTA_MAX_VDIM = 256
-DELTA_MAX_TAPS = 8
+DELTA_MAX_TAPS = 16
 
 
 def delta_shape(head_dim: int, v_dim: int) -> tuple[int, int] | None:

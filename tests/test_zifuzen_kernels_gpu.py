@@ -194,7 +194,8 @@ def _delta_run(ops, x, conv, rate_log, step_bias, norm_w, state, cuts, slot, siz
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,D,V,taps", [(2, 1, 64, 32, 4), (6, 6, 64, 32, 3), (3, 3, 16, 20, 2), (4, 2, 128, 128, 4),
-                                          (2, 1, 24, 8, 1), (2, 2, 256, 64, 2), (4, 1, 40, 256, 5), (1, 1, 8, 1, 8)])
+                                          (2, 1, 24, 8, 1), (2, 2, 256, 64, 2), (4, 1, 40, 256, 5), (1, 1, 8, 1, 8),
+                                          (2, 1, 32, 16, 12)])
 def test_delta_rule_prompt_portions_and_single_tokens_agree_with_the_plain_recurrence(dtype, H, G, D, V, taps):
     ops = _ops()
     eps, T = 1e-6, 45
