@@ -152,3 +152,16 @@ def test_a_borrowing_mixer_must_be_scheduled_behind_its_source(fake_ext):
     runner = ModelRunner(model, page_size=4, num_pages=8, max_seqs=2, cuda_graphs=False)
     with pytest.raises(ValueError, match="cache_of"):
         runner.step([SeqStep(runner.open("a"), [1, 2, 3], [2])])
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4])
+def test_random_configurations_replay(fake_ext, seed):
+    """Seeded random configurations (layer order, sizes, groups, shared experts, borrowed pages drawn anew) through
+    the engine's host side in a mixed trace."""
+    folder = zu.random_model_folder(seed)
+    raw = zu.CONFIGS[f"random{seed}"][0]
+    requests = ru.make_requests(raw["vocab"], (1, 2, 23, 61, 37), seed=seed)
+    expected = zu.plain_logits(folder, raw, requests)
+    trace = ru.trace_mixed(requests, 64 * 4, seed=seed)
+    outputs = ru.run_inprocess(folder, "float32", trace, 64 * 4, page_size=16)
+    ru.compare(trace, outputs, expected, "float32")

@@ -167,3 +167,59 @@ def decisive_requests(folder: str, raw: dict, lengths, seed: int, margin: float 
                 raise AssertionError("no decisive continuation found; lower the margin")
         out[f"r{i}"] = toks
     return out
+
+
+def random_config(seed: int) -> dict:
+    """A seeded random configuration of the design: 3 to 6 layers in any order, every size drawn anew (widths and
+    head sizes that are no multiples of 16 among them), optional groups, shared expert, feed-forward and logit cap, and
+    attention layers that read the pages of a random earlier attention layer of the same shape."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice((40, 48, 64, 72, 96, 104, 128))
+    layers, owners = [], []          # owners: (layer index, kv_heads, dim, vdim) of attention layers with their own k/v
+    for i in range(rng.randint(3, 6)):
+        if rng.random() < 0.5:
+            kv = rng.choice((1, 2, 3))
+            heads = kv * rng.choice((1, 2, 4))
+            dim = rng.choice((8, 12, 16, 24, 32, 48, 64))
+            vdim = dim if rng.random() < 0.5 else rng.choice((8, 16, 20, 32, 40))
+            source = None
+            same = [o for o in owners if rng.random() < 0.6]
+            if same:
+                j, kv, dim, vdim = rng.choice(same)
+                heads = kv * rng.choice((1, 2, 4))
+                source = j
+            else:
+                owners.append((i, kv, dim, vdim))
+            mixer = _attention(heads, kv, dim, vdim, round(rng.uniform(0.5, 2.0) * dim ** -0.5, 4), kv_from=source)
+            kind = "attention"
+        else:
+            kv = rng.choice((1, 2, 3))
+            mixer = _delta(kv * rng.choice((1, 2, 3)), kv, rng.choice((8, 12, 16, 24, 32, 64)),
+                           rng.choice((4, 8, 12, 16, 32)), rng.choice((1, 2, 3, 4, 5)))
+            kind = rng.choice(("delta", "delta_2"))
+        choice = rng.random()
+        if choice < 0.2:
+            mlp = None
+        elif choice < 0.45:
+            mlp = rng.choice((24, 40, 64, 96))
+        else:
+            count = rng.choice((1, 2, 3, 4))
+            per = rng.choice((1, 2, 3, 4))
+            keep = rng.randint(1, count)
+            experts = count * per
+            top = rng.randint(1, min(4, keep * per))
+            mlp = _moe(experts, top, rng.choice((8, 16, 24, 40)), rng.choice((0.5, 1.0, 2.0, 7.0)),
+                       round(rng.uniform(0.5, 3.0), 3), groups=(count, keep) if rng.random() < 0.7 or count > 1 else None,
+                       shared=(rng.choice((8, 16, 48)), rng.choice((0.5, 2.0))) if rng.random() < 0.6 else None)
+        layers.append(_layer(kind, mixer, mlp))
+    return {"architecture": "Zifuzen", "vocab": rng.choice((61, 128, 257)), "width": width,
+            "max_positions": 200, "embedding": {"scale": round(rng.uniform(0.5, 20.0), 3)},
+            "norm": {"eps": rng.choice((1e-5, 1e-6))}, "logit_softcap": rng.choice((None, 5.0, 30.0)), "layers": layers}
+
+
+@functools.lru_cache(maxsize=None)
+def random_model_folder(seed: int) -> str:
+    """A model folder for :func:`random_config` with the same scalings as :func:`model_folder`."""
+    CONFIGS[f"random{seed}"] = (random_config(seed), 16)
+    return model_folder(f"random{seed}", seed=seed)
