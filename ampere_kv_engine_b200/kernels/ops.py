@@ -520,7 +520,7 @@ def delta_scan(qkv, coef, x, norm_weight, state, cu_q, state_slots, *, num_heads
 # ----------------------------------------------------------------------------- routed experts
 
 MOE_MAX_EXPERTS = 512
-MOE_MAX_TOP = 16
+MOE_MAX_TOP = 32
 MOE_FORMS = {"auto": 0, "plain": 1, "mma": 2, "few": 3}
 
 

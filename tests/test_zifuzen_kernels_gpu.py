@@ -393,7 +393,7 @@ def test_sort_by_expert():
 @pytest.mark.parametrize("dtype,kernel", [(torch.float32, "auto"), (torch.bfloat16, "auto"), (torch.bfloat16, "plain"),
                                           (torch.bfloat16, "mma"), (torch.bfloat16, "few")])
 @pytest.mark.parametrize("tokens,width,inter,experts,top", [(70, 72, 40, 6, 2), (3, 48, 16, 8, 4), (150, 256, 64, 3, 1),
-                                                            (1, 100, 33, 5, 2), (200, 136, 200, 2, 2)])
+                                                            (1, 100, 33, 5, 2), (450, 136, 200, 2, 2)])
 def test_expert_products_and_sum(dtype, kernel, tokens, width, inter, experts, top):
     ops = _ops()
     if kernel in ("mma", "few") and width % 8:
